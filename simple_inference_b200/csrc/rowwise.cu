@@ -1,0 +1,151 @@
+// Row-wise kernels: embedding gather, RMSNorm with the residual add fused in,
+// and the SwiGLU gate.  All arithmetic is float32; one rounding at the store.
+//
+//   embedding   x0[t] = E[id[t]]                       reference ops/embedding.py:57-60
+//   RMSNorm     y = x * rsqrt(mean(x^2) + eps) * w     reference ops/rmsnorm.py:41-46,
+//                                                       kernels/rmsnorm_kernel.py:105-113
+//   residual    x = x + h (fused into the norm)        reference model/block.py:138,144
+//   SwiGLU      h = silu(g) * u, silu(g) = g*sigmoid(g) reference ops/mlp.py:117-125,
+//                                                       kernels/swiglu_kernel.py:142-150
+#include "common.cuh"
+
+namespace si {
+
+// ---------------------------------------------------------------- embedding
+template <typename T>
+__global__ void embed_gather_kernel(const T* __restrict__ table, const int* __restrict__ ids,
+                                    float* __restrict__ out, int hidden, int vocab) {
+  const int t = blockIdx.x;
+  const int id = ids[t];
+  float* dst = out + (size_t)t * hidden;
+  if (id < 0 || id >= vocab) {
+    // The host checks ids before a step; a bad id must still not read outside
+    // the table.  NaN makes the fault visible in the logits.
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = __int_as_float(0x7fc00000);
+    return;
+  }
+  const T* src = table + (size_t)id * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_f32<T>(src[i]);
+}
+
+// ------------------------------------------------------------------ RMSNorm
+// One block per output row r.  Source row = rows ? rows[r] : r.
+//   x = residual[src] (+ delta[src]);  if (!rows && delta) residual[src] = x;
+//   out[r] = x * rsqrt(sum(x^2)/H + eps) * w
+// The row is kept in shared memory between the two passes.
+template <typename TA, typename TW>
+__global__ void rmsnorm_kernel(float* __restrict__ residual, const TA* __restrict__ delta,
+                               const TW* __restrict__ weight, const int* __restrict__ rows,
+                               TA* __restrict__ out, int hidden, float eps) {
+  extern __shared__ float srow[];
+  __shared__ float red[32];
+  const int r = blockIdx.x;
+  const int src = rows ? rows[r] : r;
+  float* res = residual + (size_t)src * hidden;
+  const TA* del = delta ? delta + (size_t)src * hidden : nullptr;
+  const bool write_back = (rows == nullptr) && (delta != nullptr);
+  float ss = 0.0f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float x = res[i];
+    if (del) {
+      x += to_f32<TA>(del[i]);
+      if (write_back) res[i] = x;
+    }
+    srow[i] = x;
+    ss += x * x;
+  }
+  const float total = block_sum(ss, red);
+  const float rstd = rsqrtf(total / (float)hidden + eps);
+  TA* dst = out + (size_t)r * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    dst[i] = from_f32<TA>((srow[i] * rstd) * to_f32<TW>(weight[i]));
+  }
+}
+
+// ------------------------------------------------------------------- SwiGLU
+// gu is [rows, 2*inter]: gate in columns [0, inter), up in [inter, 2*inter).
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, long long total,
+                              int inter) {
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const long long row = idx / inter;
+    const int col = (int)(idx - row * inter);
+    const float g = to_f32<T>(gu[row * 2 * inter + col]);
+    const float u = to_f32<T>(gu[row * 2 * inter + inter + col]);
+    const float s = g / (1.0f + expf(-g));
+    out[idx] = from_f32<T>(s * u);
+  }
+}
+
+}  // namespace si
+
+SI_API int si_embed_gather(const void* table, int table_dtype, const int* ids, float* out,
+                           int n_tokens, int hidden, int vocab, cudaStream_t stream) {
+  if (!table || !ids || !out || n_tokens < 0 || hidden <= 0 || vocab <= 0) return SI_ERR_ARG;
+  if (n_tokens == 0) return SI_OK;
+  const int threads = hidden >= 1024 ? 256 : 128;
+  if (table_dtype == SI_F32)
+    si::embed_gather_kernel<float><<<n_tokens, threads, 0, stream>>>(
+        (const float*)table, ids, out, hidden, vocab);
+  else if (table_dtype == SI_BF16)
+    si::embed_gather_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(
+        (const __nv_bfloat16*)table, ids, out, hidden, vocab);
+  else
+    return SI_ERR_DTYPE;
+  SI_LAUNCH_CHECK();
+  return SI_OK;
+}
+
+template <typename TA, typename TW>
+static int launch_rmsnorm(float* residual, const void* delta, const void* weight, const int* rows,
+                          void* out, int n_rows, int hidden, float eps, cudaStream_t stream) {
+  const size_t smem = (size_t)hidden * sizeof(float);
+  if (smem > 200 * 1024) return SI_ERR_TOO_LARGE;
+  auto kern = si::rmsnorm_kernel<TA, TW>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+  }
+  const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+  kern<<<n_rows, threads, smem, stream>>>(residual, (const TA*)delta, (const TW*)weight, rows,
+                                          (TA*)out, hidden, eps);
+  SI_LAUNCH_CHECK();
+  return SI_OK;
+}
+
+// act_dtype: dtype of delta and out.  weight_dtype: dtype of the gain.
+SI_API int si_rmsnorm(float* residual, const void* delta, const void* weight, const int* rows,
+                      void* out, int n_rows, int hidden, float eps, int act_dtype,
+                      int weight_dtype, cudaStream_t stream) {
+  if (!residual || !weight || !out || n_rows < 0 || hidden <= 0 || !(eps > 0.0f)) return SI_ERR_ARG;
+  if (n_rows == 0) return SI_OK;
+  if (act_dtype == SI_F32 && weight_dtype == SI_F32)
+    return launch_rmsnorm<float, float>(residual, delta, weight, rows, out, n_rows, hidden, eps, stream);
+  if (act_dtype == SI_BF16 && weight_dtype == SI_F32)
+    return launch_rmsnorm<__nv_bfloat16, float>(residual, delta, weight, rows, out, n_rows, hidden, eps, stream);
+  if (act_dtype == SI_BF16 && weight_dtype == SI_BF16)
+    return launch_rmsnorm<__nv_bfloat16, __nv_bfloat16>(residual, delta, weight, rows, out, n_rows, hidden, eps, stream);
+  if (act_dtype == SI_F32 && weight_dtype == SI_BF16)
+    return launch_rmsnorm<float, __nv_bfloat16>(residual, delta, weight, rows, out, n_rows, hidden, eps, stream);
+  return SI_ERR_DTYPE;
+}
+
+SI_API int si_swiglu(const void* gu, void* out, int n_rows, int inter, int dtype,
+                     cudaStream_t stream) {
+  if (!gu || !out || n_rows < 0 || inter <= 0) return SI_ERR_ARG;
+  if (n_rows == 0) return SI_OK;
+  const long long total = (long long)n_rows * inter;
+  const int threads = 256;
+  long long blocks = (total + threads - 1) / threads;
+  if (blocks > 148LL * 32) blocks = 148LL * 32;
+  if (dtype == SI_F32)
+    si::swiglu_kernel<float><<<(int)blocks, threads, 0, stream>>>((const float*)gu, (float*)out, total, inter);
+  else if (dtype == SI_BF16)
+    si::swiglu_kernel<__nv_bfloat16><<<(int)blocks, threads, 0, stream>>>(
+        (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, total, inter);
+  else
+    return SI_ERR_DTYPE;
+  SI_LAUNCH_CHECK();
+  return SI_OK;
+}

@@ -1,0 +1,162 @@
+"""A model as data: parts chosen layer by layer, and the order layers run in.
+
+An architecture module turns its typed configuration into a ``ModelPlan``:
+the embedding, a list of ``LayerPlan`` (each a block ``PartSpec`` plus the
+checkpoint name of every tensor it needs), the run order, the final norm and
+the output head.  ``DecoderModel`` builds the parts through the registries,
+binds the loaded tensors and executes the plan for a step; it knows nothing of
+any particular architecture.
+
+The run order is a list of ``RunStep``.  A step names a layer (a layer may be
+named more than once: the same weights run again, each run with a cache entry
+of its own) and the cache entry it uses; ``writes_cache=False`` lets a run read
+the entry another run filled instead of storing its own keys and values.
+
+The reference fixes all of this in code: 28 identical ``TransformerBlock``s run
+in index order (``model/llama.py:92-106,174-186``).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+
+from ..parts.base import Block, CacheSpec, LayerCache, PartSpec, Runtime, TensorSpec
+from ..parts.embedding import OutputHead, TokenEmbedding
+from ..parts.registry import BLOCKS, NORMS
+
+
+@dataclass
+class LayerPlan:
+    block: PartSpec
+    # part-local tensor name ("mixer.wq") -> name in the checkpoint
+    tensor_names: dict[str, str]
+
+
+@dataclass(frozen=True)
+class RunStep:
+    layer: int
+    cache_entry: int
+    writes_cache: bool = True
+
+
+@dataclass
+class ModelPlan:
+    hidden_size: int
+    vocab_size: int
+    layers: list[LayerPlan]
+    run_order: list[RunStep]
+    final_norm: PartSpec
+    tie_embeddings: bool
+    embedding_name: str
+    final_norm_names: dict[str, str]
+    head_name: str | None
+    max_positions: int
+    eos_token_ids: tuple[int, ...] = ()
+    bos_token_id: int | None = None
+
+    @staticmethod
+    def sequential(num_layers: int) -> list[RunStep]:
+        return [RunStep(i, i, True) for i in range(num_layers)]
+
+
+@dataclass
+class CacheEntryInfo:
+    """Cache need of one cache entry of the run order."""
+    spec: CacheSpec | None
+    writer: int | None = None  # index into run_order of the run that fills it
+
+
+class DecoderModel:
+    """Executes a ``ModelPlan``: embedding, blocks in run order, final norm, head."""
+
+    def __init__(self, plan: ModelPlan):
+        self.plan = plan
+        self.embedding = TokenEmbedding(plan.vocab_size, plan.hidden_size)
+        self.blocks: list[Block] = [BLOCKS.build(lp.block) for lp in plan.layers]
+        self.final_norm = NORMS.build(plan.final_norm)
+        self.head = OutputHead(plan.vocab_size, plan.hidden_size, plan.tie_embeddings)
+        self.rt: Runtime | None = None
+        self._check_run_order()
+
+    # ------------------------------------------------------------ structure
+    def _check_run_order(self) -> None:
+        n_layers = len(self.blocks)
+        entries: dict[int, CacheEntryInfo] = {}
+        for idx, step in enumerate(self.plan.run_order):
+            if not (0 <= step.layer < n_layers):
+                raise ValueError(f"run order names layer {step.layer}, the model has {n_layers}")
+            spec = self.blocks[step.layer].mixer.cache_spec()
+            info = entries.get(step.cache_entry)
+            if info is None:
+                if not step.writes_cache and spec is not None:
+                    raise ValueError(f"run {idx} reads cache entry {step.cache_entry} "
+                                     f"before any run has written it")
+                entries[step.cache_entry] = CacheEntryInfo(spec, idx)
+            else:
+                if step.writes_cache:
+                    raise ValueError(f"runs {info.writer} and {idx} both write cache entry "
+                                     f"{step.cache_entry}")
+                if info.spec != spec:
+                    raise ValueError(f"run {idx} reads cache entry {step.cache_entry} whose "
+                                     f"shape {info.spec} differs from its own {spec}")
+        if sorted(entries) != list(range(len(entries))):
+            raise ValueError("cache entries of the run order must be numbered 0..n-1")
+        self.cache_entries = [entries[i] for i in range(len(entries))]
+
+    def cache_specs(self) -> list[CacheSpec | None]:
+        """Cache need of every cache entry, in entry order (for the cache manager)."""
+        return [e.spec for e in self.cache_entries]
+
+    def tensor_specs(self) -> dict[str, TensorSpec]:
+        """Checkpoint tensor name -> spec, for the loader and the random-weights writer."""
+        out: dict[str, TensorSpec] = {
+            self.plan.embedding_name: self.embedding.tensors()["weight"],
+        }
+        for lp, block in zip(self.plan.layers, self.blocks):
+            for local, spec in block.tensors().items():
+                out[lp.tensor_names[local]] = spec
+        for local, spec in self.final_norm.tensors().items():
+            out[self.plan.final_norm_names[local]] = spec
+        if not self.plan.tie_embeddings:
+            out[self.plan.head_name] = self.head.tensors()["weight"]
+        return out
+
+    def optional_tensor_names(self) -> set[str]:
+        """Names a checkpoint may carry that the model does not need."""
+        if self.plan.tie_embeddings and self.plan.head_name:
+            return {self.plan.head_name}  # a tied checkpoint may still store the head
+        return set()
+
+    # -------------------------------------------------------------- weights
+    def bind(self, tensors: dict[str, torch.Tensor], rt: Runtime) -> None:
+        """``tensors``: checkpoint name -> device tensor in its final dtype."""
+        self.rt = rt
+        self.embedding.bind({"weight": tensors[self.plan.embedding_name]}, rt)
+        for lp, block in zip(self.plan.layers, self.blocks):
+            block.bind({local: tensors[name] for local, name in lp.tensor_names.items()}, rt)
+        self.final_norm.bind({local: tensors[name]
+                              for local, name in self.plan.final_norm_names.items()}, rt)
+        head_t = {} if self.plan.tie_embeddings else {"weight": tensors[self.plan.head_name]}
+        self.head.bind(head_t, rt, embedding=self.embedding)
+
+    # ----------------------------------------------------------------- step
+    def forward(self, ctx, caches: list[LayerCache | None]) -> torch.Tensor:
+        """Run the tokens of ``ctx``; return float32 logits at ``ctx.logit_rows``.
+
+        ``caches[e]`` is the view of cache entry ``e``.
+        """
+        residual = self.embedding.forward(ctx.token_ids, ctx)
+        delta = None
+        for step in self.plan.run_order:
+            cache = caches[step.cache_entry]
+            if cache is not None and cache.writes != step.writes_cache:
+                cache = LayerCache(cache.spec, cache.group, cache.pool, cache.state,
+                                   cache.page_size, step.writes_cache)
+            delta = self.blocks[step.layer].forward(residual, delta, ctx, cache)
+        if ctx.num_logit_rows == 0:
+            return ctx.ws.get("logits", (0, self.plan.vocab_size), torch.float32,
+                              row_cap=ctx.ws.max_logit_rows)
+        h = self.final_norm.add_forward(residual, delta, ctx, rows=ctx.logit_rows, tag="final_norm")
+        return self.head.forward(h, ctx)

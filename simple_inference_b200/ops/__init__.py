@@ -1,0 +1,257 @@
+"""Python face of the sm_100a kernels.
+
+Each function checks its tensors, then calls one ``extern "C"`` launcher of the
+compiled library on the current CUDA stream.  There is no other implementation
+behind these names: a tensor that is not on a CUDA device, or a library that
+cannot be built, raises.
+
+bfloat16 matrix products call the library GEMM (cuBLAS through ``torch.mm``),
+as the reference's engine does for every linear layer (``F.linear``,
+``ops/attention.py:128-130``, ``ops/mlp.py:117,128``, ``ops/embedding.py:92``);
+float32 products run the hand-written FMA kernel, never a tensor-core mode.
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from .build import KernelBuildError, load_library
+
+_CORE_SOURCES = ["rowwise.cu", "rope_kv.cu", "gemm_fp32.cu", "attention_generic.cu",
+                 "sampling.cu", "attention_decode.cu", "no_alloc.cu"]
+
+_ERRORS = {
+    -1: "bad argument (null pointer, negative size or misaligned pointer)",
+    -2: "a size this kernel does not take",
+    -3: "a dtype this kernel does not take",
+    -4: "a size beyond the kernel's stated maximum",
+}
+
+_c_int, _c_float, _c_void_p = ctypes.c_int, ctypes.c_float, ctypes.c_void_p
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def core_sources() -> list[str]:
+    from .build import CSRC
+    return [s for s in _CORE_SOURCES if (CSRC / s).is_file()]
+
+
+def core() -> ctypes.CDLL:
+    return load_library("si_core", core_sources())
+
+
+def attention_library(head_dim: int) -> ctypes.CDLL:
+    """Tensor-core attention kernels are compiled for one head size at a time."""
+    if head_dim % 16 != 0 or not (16 <= head_dim <= 256):
+        raise KernelError(
+            f"head_dim {head_dim}: the attention kernels take multiples of 16 from 16 to 256"
+        )
+    return load_library(f"si_attn_d{head_dim}", ["attention_mma.cu"], [f"-DSI_HEAD_DIM={head_dim}"])
+
+
+def _check(code: int, what: str) -> None:
+    if code == 0:
+        return
+    if code < 0:
+        raise KernelError(f"{what}: refused, {_ERRORS.get(code, code)}")
+    raise KernelError(f"{what}: CUDA error {code} at launch")
+
+
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return 0
+    if t.dtype == torch.bfloat16:
+        return 1
+    raise KernelError(f"dtype {t.dtype} is not float32 or bfloat16")
+
+
+def _dev(*tensors: torch.Tensor | None) -> None:
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise KernelError("kernel called with a tensor that is not on a CUDA device; "
+                              "there is no CPU path")
+        if not t.is_contiguous():
+            raise KernelError(f"kernel called with a non-contiguous tensor of shape {tuple(t.shape)}")
+
+
+def _p(t: torch.Tensor | None) -> ctypes.c_void_p:
+    return _c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream() -> ctypes.c_void_p:
+    return _c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _i32(t: torch.Tensor | None, name: str) -> None:
+    if t is not None and t.dtype != torch.int32:
+        raise KernelError(f"{name} must be int32, is {t.dtype}")
+
+
+# ----------------------------------------------------------------- row-wise
+
+def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """``out[t] = table[ids[t]]`` as float32 (the residual stream)."""
+    _dev(table, ids, out)
+    _i32(ids, "ids")
+    n, hidden = out.shape
+    if out.dtype != torch.float32 or table.shape[1] != hidden or ids.numel() < n:
+        raise KernelError("embed_gather: shape or dtype mismatch")
+    _check(core().si_embed_gather(_p(table), _dt(table), _p(ids), _p(out), n, hidden,
+                                  table.shape[0], _stream()), "embed_gather")
+    return out
+
+
+def rmsnorm(residual: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
+            delta: torch.Tensor | None = None, rows: torch.Tensor | None = None) -> torch.Tensor:
+    """RMSNorm of rows of the float32 residual, with the pending add fused in.
+
+    Without ``rows``: ``residual += delta`` (if given) in place, ``out = norm(residual)``.
+    With ``rows``: ``out[r] = norm(residual[rows[r]] + delta[rows[r]])``, residual untouched.
+    """
+    _dev(residual, weight, out, delta, rows)
+    _i32(rows, "rows")
+    n_rows, hidden = out.shape
+    if residual.dtype != torch.float32 or residual.shape[1] != hidden or weight.numel() != hidden:
+        raise KernelError("rmsnorm: shape or dtype mismatch")
+    if delta is not None and (delta.dtype != out.dtype or delta.shape[1] != hidden):
+        raise KernelError("rmsnorm: delta must have the dtype of out and the width of residual")
+    if rows is None and residual.shape[0] < n_rows:
+        raise KernelError("rmsnorm: fewer residual rows than output rows")
+    if rows is not None and rows.numel() < n_rows:
+        raise KernelError("rmsnorm: fewer row indices than output rows")
+    _check(core().si_rmsnorm(_p(residual), _p(delta), _p(weight), _p(rows), _p(out), n_rows,
+                             hidden, _c_float(eps), _dt(out), _dt(weight), _stream()), "rmsnorm")
+    return out
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """``out = silu(gate_up[:, :I]) * gate_up[:, I:]`` in float32 arithmetic."""
+    _dev(gate_up, out)
+    n, inter = out.shape
+    if gate_up.shape != (n, 2 * inter) or gate_up.dtype != out.dtype:
+        raise KernelError("swiglu: shape or dtype mismatch")
+    _check(core().si_swiglu(_p(gate_up), _p(out), n, inter, _dt(out), _stream()), "swiglu")
+    return out
+
+
+# ------------------------------------------------------------ matrix product
+
+def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """``out = x @ weight.T`` for ``weight`` in the ``[out, in]`` layout.
+
+    float32 operands: the FMA kernel (true 32-bit).  bfloat16 operands: the
+    library GEMM with float32 accumulation; ``out`` may be bfloat16 or float32.
+    """
+    _dev(x, weight, out)
+    m, k = x.shape
+    n = weight.shape[0]
+    if weight.shape[1] != k or out.shape != (m, n) or x.dtype != weight.dtype:
+        raise KernelError(f"linear: shapes {tuple(x.shape)} x {tuple(weight.shape)} -> "
+                          f"{tuple(out.shape)} or dtypes do not fit")
+    if x.dtype == torch.float32:
+        if out.dtype != torch.float32:
+            raise KernelError("linear: float32 operands need a float32 output")
+        _check(core().si_gemm_fp32_tn(_p(x), _p(weight), _p(out), m, n, k, k, k, n, _stream()),
+               "gemm_fp32")
+    elif out.dtype == torch.bfloat16:
+        torch.mm(x, weight.t(), out=out)
+    else:
+        torch.mm(x, weight.t(), out_dtype=torch.float32, out=out)
+    return out
+
+
+# ------------------------------------------------------ positions and cache
+
+def rope_kv_store(qkv: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor,
+                  kv_slots: torch.Tensor | None, pool: torch.Tensor | None, num_q_heads: int,
+                  num_kv_heads: int, head_dim: int, page_size: int, write_kv: bool) -> None:
+    """Rotate q (in place) and k, and write k, v of every token into its page slot."""
+    _dev(qkv, positions, inv_freq, kv_slots, pool)
+    _i32(positions, "positions")
+    _i32(kv_slots, "kv_slots")
+    n = qkv.shape[0]
+    if qkv.shape[1] != (num_q_heads + 2 * num_kv_heads) * head_dim:
+        raise KernelError("rope_kv_store: qkv width does not fit the head counts")
+    if inv_freq.dtype != torch.float32 or inv_freq.numel() != head_dim // 2:
+        raise KernelError("rope_kv_store: inv_freq must be float32 of head_dim/2 entries")
+    if write_kv:
+        if pool is None or kv_slots is None or pool.dtype != qkv.dtype:
+            raise KernelError("rope_kv_store: pool and kv_slots needed, pool in qkv's dtype")
+        if tuple(pool.shape[1:]) != (2, num_kv_heads, page_size, head_dim):
+            raise KernelError(f"rope_kv_store: pool shape {tuple(pool.shape)} does not fit")
+    _check(core().si_rope_kv_store(_p(qkv), _p(positions), _p(inv_freq), _p(kv_slots), _p(pool), n,
+                                   num_q_heads, num_kv_heads, head_dim, page_size,
+                                   1 if write_kv else 0, _dt(qkv), _stream()), "rope_kv_store")
+
+
+# ---------------------------------------------------------------- attention
+
+def attention_generic(q: torch.Tensor, pool: torch.Tensor, block_table: torch.Tensor,
+                      tok_seq: torch.Tensor, positions: torch.Tensor, out: torch.Tensor,
+                      num_q_heads: int, num_kv_heads: int, head_dim: int, scale: float,
+                      window: int | None) -> torch.Tensor:
+    """Attention of every token over its request's pages, float32 arithmetic.
+
+    ``q`` may be the fused qkv buffer: only its first ``num_q_heads*head_dim``
+    columns are read, with its own row stride.
+    """
+    _dev(pool, block_table, tok_seq, positions, out)
+    if not q.is_cuda or q.stride(1) != 1:
+        raise KernelError("attention: q must be a CUDA tensor with unit inner stride")
+    _i32(block_table, "block_table"); _i32(tok_seq, "tok_seq"); _i32(positions, "positions")
+    n = out.shape[0]
+    page_size = pool.shape[3]
+    if tuple(pool.shape[1:]) != (2, num_kv_heads, page_size, head_dim) or pool.dtype != q.dtype \
+            or out.dtype != q.dtype:
+        raise KernelError("attention: pool/out shape or dtype does not fit")
+    _check(core().si_attention_generic(
+        _p(q), q.stride(0), _p(pool), _p(block_table), block_table.stride(0), _p(tok_seq),
+        _p(positions), _p(out), out.stride(0), n, num_q_heads, num_kv_heads, head_dim, page_size,
+        _c_float(scale), int(window or 0), _dt(q), _stream()), "attention_generic")
+    return out
+
+
+def paged_attention(q: torch.Tensor, pool: torch.Tensor, ctx, group: int, out: torch.Tensor,
+                    num_q_heads: int, num_kv_heads: int, head_dim: int, scale: float,
+                    window: int | None) -> torch.Tensor:
+    """Attention of a step's tokens over the pages of layer group ``group``.
+
+    ``ctx`` is the step's ``StepContext``.  float32: the generic kernel for every
+    token.  bfloat16: tensor-core kernels, one for sequences that bring a single
+    token (split over the keys) and one for longer portions (64-query tiles).
+    """
+    return attention_generic(q, pool, ctx.block_tables[group], ctx.tok_seq, ctx.positions, out,
+                             num_q_heads, num_kv_heads, head_dim, scale, window)
+
+
+# ----------------------------------------------------------------- sampling
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
+           top_p: torch.Tensor, seed: torch.Tensor, stream_id: torch.Tensor,
+           counter: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """One token per row of float32 logits; per-row parameters (see sampling.cu)."""
+    _dev(logits, temperature, top_k, top_p, seed, stream_id, counter, out)
+    n, vocab = logits.shape
+    if logits.dtype != torch.float32 or temperature.dtype != torch.float32 or \
+            top_p.dtype != torch.float32:
+        raise KernelError("sample: logits, temperature and top_p must be float32")
+    for name, t in (("top_k", top_k), ("seed", seed), ("stream_id", stream_id),
+                    ("counter", counter), ("out", out)):
+        _i32(t, name)
+        if t.numel() < n:
+            raise KernelError(f"sample: {name} has fewer than {n} entries")
+    _check(core().si_sample(_p(logits), n, vocab, logits.stride(0), _p(temperature), _p(top_k),
+                            _p(top_p), _p(seed), _p(stream_id), _p(counter), _p(out), _stream()),
+           "sample")
+    return out
+
+
+__all__ = ["KernelError", "KernelBuildError", "embed_gather", "rmsnorm", "swiglu", "linear",
+           "rope_kv_store", "attention_generic", "paged_attention", "sample", "core", "attention_library"]
