@@ -67,6 +67,17 @@ class PageAllocator:
         self._reserved[owner] = count
         self._owned[owner] = set()
 
+    def reserve_more(self, owner: Hashable, count: int) -> None:
+        """Promise ``count`` further pages to an owner that already holds a reservation."""
+        if owner not in self._reserved:
+            raise KeyError(f"owner {owner!r} holds no reservation")
+        if count < 0:
+            raise ValueError(f"cannot reserve {count} pages")
+        if count > self.available:
+            raise OutOfPages(f"cannot reserve {count} more pages for {owner!r}: "
+                             f"{self.available} left")
+        self._reserved[owner] += count
+
     def allocate(self, owner: Hashable) -> int:
         if owner not in self._reserved:
             raise KeyError(f"owner {owner!r} holds no reservation")

@@ -144,6 +144,27 @@ class CacheManager:
             t[slot].zero_()
         return slot
 
+    def reserve_to(self, request: Hashable, total_tokens: int) -> None:
+        """Raise an admitted request's reservation so that it can reach ``total_tokens``.
+
+        For callers that do not know a request's final length when they admit
+        it (trace replay).  Raises ``OutOfPages`` when the pool cannot promise it.
+        """
+        for g in self.groups:
+            need = g.pages_needed(total_tokens, self.max_step_tokens)
+            rp = g.requests[request]
+            live = sum(1 for p in rp.table if p >= 0)
+            have = live + g.allocator._reserved[request]
+            if need > have and need - have > g.allocator.available:
+                raise OutOfPages(f"request {request!r} cannot grow to {total_tokens} tokens: "
+                                 f"group {g.index} has {g.allocator.available} pages to promise")
+        for g in self.groups:
+            need = g.pages_needed(total_tokens, self.max_step_tokens)
+            rp = g.requests[request]
+            have = sum(1 for p in rp.table if p >= 0) + g.allocator._reserved[request]
+            if need > have:
+                g.allocator.reserve_more(request, need - have)
+
     def release(self, request: Hashable) -> None:
         """Give back every page and the slot of a finished request."""
         if request not in self._slot_of:
