@@ -1,0 +1,556 @@
+// Tensor-core attention over the paged cache for bfloat16, compiled for one
+// head size (-DSI_HEAD_DIM=D, D a multiple of 16 up to 256).
+//
+// Two kernels share one tile loader and one softmax recurrence:
+//
+//   attn_prefill_kernel  one block per (64-query tile of a sequence, query head):
+//                        the flash-attention forward of the reference
+//                        (kernels/attention_kernel.py:108-251) reading keys and
+//                        values through the block table instead of a gathered copy
+//                        (serving/paged_kv_cache.py:188-256).
+//   attn_decode_kernel   sequences that bring one token: one block per (sequence,
+//                        key/value head, split of the keys); the G query heads of
+//                        the group are the rows of one 16-row tile, so keys and
+//                        values are read once per group, not once per head, and
+//                        the keys are split over blocks (the reference's paged
+//                        decode, kernels/attention_kernel.py:496-586, has one
+//                        program per query head and no split).  Partial results
+//                        go to scratch memory and attn_merge_kernel joins them.
+//
+// Both compute S = (Q K^T) * scale with mma.sync m16n8k16 (bf16 in, float32
+// accumulate), mask by absolute position (key j visible to a query at position
+// p iff p - window < j <= p), run the online softmax in float32
+// (kernels/attention_kernel.py:231-241: m' = max(m, rowmax), P = exp(S - m'),
+// l = l*exp(m-m') + sum P, acc = acc*exp(m-m') + P V), round P to bfloat16 for
+// the P V product as the reference does (:240), and divide by l at the end.
+// Key tiles are 64 keys aligned to absolute key index, so the order of every
+// sum depends on key indices only.
+//
+// Shared-memory rows are padded by 16 bytes: the row stride is then an odd
+// multiple of 16 bytes modulo 128, which makes every ldmatrix conflict-free for
+// any D that is a multiple of 16.
+#include "common.cuh"
+
+#ifndef SI_HEAD_DIM
+#error "compile with -DSI_HEAD_DIM=<head size>"
+#endif
+
+namespace si {
+
+constexpr int D = SI_HEAD_DIM;
+static_assert(D % 16 == 0 && D >= 16 && D <= 256, "head size must be a multiple of 16 in [16, 256]");
+constexpr int STRIDE = D + 8;        // elements per shared-memory row
+constexpr int KV_TILE = 64;          // keys per tile
+constexpr int Q_TILE = 64;           // query rows per prefill block
+constexpr int THREADS = 128;
+constexpr int CHUNKS = D / 8;        // 16-byte chunks per row
+constexpr float LOG2E = 1.4426950408889634f;
+
+typedef __nv_bfloat16 bf16;
+
+// ------------------------------------------------------------------ PTX helpers
+__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  const int bytes = valid ? 16 : 0;  // 0: the 16 bytes are filled with zeros
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(bytes));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* p) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], const void* p) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0,
+                                         uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, "
+      "{%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// --------------------------------------------------------------- tile loader
+// Keys [key0, key0+64) of one sequence and one kv head into sK, sV.  Keys
+// outside [k_lo, k_hi] are zero-filled and their pages are not touched (a page
+// before the window may already belong to someone else).
+__device__ __forceinline__ void load_kv_tile(bf16* sK, bf16* sV, const bf16* __restrict__ pool,
+                                             const int* __restrict__ table, int key0, int k_lo,
+                                             int k_hi, int kvh, int n_kv_heads, int page_size) {
+  const int tid = threadIdx.x;
+  const int row = tid >> 1, half = tid & 1;
+  const int j = key0 + row;
+  const bool valid = (j >= k_lo) && (j <= k_hi);
+  const bf16* kptr = pool;
+  const bf16* vptr = pool;
+  if (valid) {
+    const int lp = j / page_size;
+    const int page = table[lp];
+    const int off = j - lp * page_size;
+    const long long head_stride = (long long)page_size * D;
+    kptr = pool + ((long long)page * 2 * n_kv_heads + kvh) * head_stride + (long long)off * D;
+    vptr = kptr + (long long)n_kv_heads * head_stride;
+  }
+  bf16* dk = sK + row * STRIDE;
+  bf16* dv = sV + row * STRIDE;
+#pragma unroll
+  for (int c = 0; c < CHUNKS / 2; ++c) {
+    const int chunk = half * (CHUNKS / 2) + c;
+    cp_async16(dk + chunk * 8, kptr + (valid ? chunk * 8 : 0), valid);
+    cp_async16(dv + chunk * 8, vptr + (valid ? chunk * 8 : 0), valid);
+  }
+}
+
+// One warp's S = Q_rows K_keys^T for 16 query rows and NT*8 keys.
+// sQrow0: first of the 16 query rows in shared memory; sKrow0: first key row.
+template <int NT>
+__device__ __forceinline__ void qk_tile(float (&s)[NT][4], const bf16* sQrow0, const bf16* sKrow0) {
+  static_assert(NT % 2 == 0, "n-tiles come in pairs");
+  const int lane = threadIdx.x & 31;
+#pragma unroll
+  for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) s[nt][e] = 0.0f;
+#pragma unroll
+  for (int ks = 0; ks < D / 16; ++ks) {
+    uint32_t a[4];
+    ldsm_x4(a, sQrow0 + ((lane & 7) + 8 * ((lane >> 3) & 1)) * STRIDE + ks * 16 + 8 * (lane >> 4));
+#pragma unroll
+    for (int np = 0; np < NT / 2; ++np) {
+      uint32_t b[4];
+      ldsm_x4(b, sKrow0 + (np * 16 + (lane & 7) + 8 * (lane >> 4)) * STRIDE + ks * 16 +
+                     8 * ((lane >> 3) & 1));
+      mma_bf16(s[2 * np], a, b[0], b[1]);
+      mma_bf16(s[2 * np + 1], a, b[2], b[3]);
+    }
+  }
+}
+
+// o += P V for one warp: P is 16 rows x NT*8 keys (already exponentiated, in s),
+// V rows start at sVrow0.
+template <int NT>
+__device__ __forceinline__ void pv_tile(float (&o)[D / 8][4], const float (&s)[NT][4],
+                                        const bf16* sVrow0) {
+  const int lane = threadIdx.x & 31;
+#pragma unroll
+  for (int kk = 0; kk < NT / 2; ++kk) {
+    uint32_t a[4];
+    a[0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+    a[1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+    a[2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+    a[3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+#pragma unroll
+    for (int dp = 0; dp < D / 16; ++dp) {
+      uint32_t b[4];
+      ldsm_x4_trans(b, sVrow0 + (kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * STRIDE + dp * 16 +
+                           8 * (lane >> 4));
+      mma_bf16(o[2 * dp], a, b[0], b[1]);
+      mma_bf16(o[2 * dp + 1], a, b[2], b[3]);
+    }
+  }
+}
+
+// Online-softmax update of one warp's rows.  s holds scaled, masked scores in
+// the log2 domain (-inf where masked) and is overwritten with P.  m, l are per
+// thread for its two rows (lane/4 and lane/4 + 8); l is the thread's partial sum.
+template <int NT>
+__device__ __forceinline__ void softmax_update(float (&s)[NT][4], float (&m)[2], float (&l)[2],
+                                               float (&o)[D / 8][4]) {
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    float mx = -INFINITY;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) mx = fmaxf(mx, fmaxf(s[nt][2 * r], s[nt][2 * r + 1]));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+    const float m_new = fmaxf(m[r], mx);
+    const float m_use = (m_new == -INFINITY) ? 0.0f : m_new;  // row fully masked so far
+    const float alpha = exp2f(m[r] - m_use);                  // m = -inf gives 0
+    float sum = 0.0f;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const float p0 = exp2f(s[nt][2 * r] - m_use);
+      const float p1 = exp2f(s[nt][2 * r + 1] - m_use);
+      s[nt][2 * r] = p0;
+      s[nt][2 * r + 1] = p1;
+      sum += p0 + p1;
+    }
+    l[r] = l[r] * alpha + sum;
+    m[r] = m_new;
+#pragma unroll
+    for (int dt = 0; dt < D / 8; ++dt) {
+      o[dt][2 * r] *= alpha;
+      o[dt][2 * r + 1] *= alpha;
+    }
+  }
+}
+
+// ------------------------------------------------------------------- prefill
+__global__ void __launch_bounds__(THREADS)
+attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ pool,
+                    const int* __restrict__ block_table, int table_stride,
+                    const int* __restrict__ cu_q, const int* __restrict__ positions,
+                    const int* __restrict__ tile_seq, const int* __restrict__ tile_start,
+                    bf16* __restrict__ out, int out_stride, int n_q_heads, int n_kv_heads,
+                    int page_size, float scale_log2, int window) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* sQ = reinterpret_cast<bf16*>(smem_raw);          // [Q_TILE][STRIDE]
+  bf16* sKV = sQ + Q_TILE * STRIDE;                      // 2 stages x (K, V) x [KV_TILE][STRIDE]
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int seq = tile_seq[blockIdx.x];
+  const int tok0 = cu_q[seq] + tile_start[blockIdx.x];
+  int n_rows = cu_q[seq + 1] - tok0;
+  if (n_rows > Q_TILE) n_rows = Q_TILE;
+  const int h = blockIdx.y;
+  const int kvh = h / (n_q_heads / n_kv_heads);
+  const int pos0 = positions[tok0];  // rows of a tile are consecutive positions
+  const int k_hi = pos0 + n_rows - 1;
+  const int k_lo = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
+  const int* table = block_table + (long long)seq * table_stride;
+
+  {  // Q tile; rows past n_rows are zero
+    const int row = tid >> 1, half = tid & 1;
+    const bool valid = row < n_rows;
+    const bf16* src = q + (long long)(tok0 + (valid ? row : 0)) * q_stride + (long long)h * D;
+#pragma unroll
+    for (int c = 0; c < CHUNKS / 2; ++c) {
+      const int chunk = half * (CHUNKS / 2) + c;
+      cp_async16(sQ + row * STRIDE + chunk * 8, src + chunk * 8, valid);
+    }
+  }
+  const int tile_first = k_lo / KV_TILE, tile_last = k_hi / KV_TILE;
+  load_kv_tile(sKV, sKV + KV_TILE * STRIDE, pool, table, tile_first * KV_TILE, k_lo, k_hi, kvh,
+               n_kv_heads, page_size);
+  cp_async_commit();
+
+  float o[D / 8][4];
+#pragma unroll
+  for (int dt = 0; dt < D / 8; ++dt)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[dt][e] = 0.0f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
+
+  for (int tile = tile_first; tile <= tile_last; ++tile) {
+    const int stage = (tile - tile_first) & 1;
+    bf16* sK = sKV + stage * 2 * KV_TILE * STRIDE;
+    bf16* sV = sK + KV_TILE * STRIDE;
+    if (tile < tile_last) {
+      bf16* nK = sKV + (stage ^ 1) * 2 * KV_TILE * STRIDE;
+      load_kv_tile(nK, nK + KV_TILE * STRIDE, pool, table, (tile + 1) * KV_TILE, k_lo, k_hi, kvh,
+                   n_kv_heads, page_size);
+      cp_async_commit();
+      cp_async_wait<1>();
+    } else {
+      cp_async_wait<0>();
+    }
+    __syncthreads();
+
+    // A warp whose 16 rows are all past n_rows, or all before this tile's keys
+    // (causal), still takes part in the barriers but skips the arithmetic.
+    const int row_lo = warp * 16;
+    const bool active = row_lo < n_rows && (pos0 + min(row_lo + 15, n_rows - 1)) >= tile * KV_TILE;
+    if (active) {
+      float s[KV_TILE / 8][4];
+      qk_tile<KV_TILE / 8>(s, sQ + row_lo * STRIDE, sK);
+      const int key0 = tile * KV_TILE;
+#pragma unroll
+      for (int nt = 0; nt < KV_TILE / 8; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int row = row_lo + (lane >> 2) + 8 * (e >> 1);
+          const int j = key0 + nt * 8 + (lane & 3) * 2 + (e & 1);
+          const int p = pos0 + row;
+          const bool ok = row < n_rows && j <= p && (window <= 0 || j > p - window);
+          s[nt][e] = ok ? s[nt][e] * scale_log2 : -INFINITY;
+        }
+      softmax_update<KV_TILE / 8>(s, m, l, o);
+      pv_tile<KV_TILE / 8>(o, s, sV);
+    }
+    __syncthreads();  // this stage is refilled by the load issued in the next iteration
+  }
+
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    float lt = l[r];
+    lt += __shfl_xor_sync(0xffffffffu, lt, 1);
+    lt += __shfl_xor_sync(0xffffffffu, lt, 2);
+    const int row = warp * 16 + (lane >> 2) + 8 * r;
+    if (row < n_rows) {
+      const float inv = 1.0f / lt;  // the query's own key is always visible, so lt > 0
+      bf16* dst = out + (long long)(tok0 + row) * out_stride + (long long)h * D + (lane & 3) * 2;
+#pragma unroll
+      for (int dt = 0; dt < D / 8; ++dt) {
+        *reinterpret_cast<__nv_bfloat162*>(dst + dt * 8) =
+            __floats2bfloat162_rn(o[dt][2 * r] * inv, o[dt][2 * r + 1] * inv);
+      }
+    }
+  }
+}
+
+// -------------------------------------------------------------------- decode
+// grid (sequences with one token, kv heads * head chunks, splits).  Rows of the
+// 16-row tile are the query heads kvh*G + chunk*16 + r.  Warp w works on keys
+// [16w, 16w+16) of every 64-key tile of this block's split; the four warps'
+// states are merged in shared memory.  With n_splits > 1 the block writes
+// (m, l, unnormalised acc) to scratch for attn_merge_kernel.
+__global__ void __launch_bounds__(THREADS)
+attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ pool,
+                   const int* __restrict__ block_table, int table_stride,
+                   const int* __restrict__ cu_q, const int* __restrict__ positions,
+                   const int* __restrict__ single_seqs, bf16* __restrict__ out, int out_stride,
+                   float* __restrict__ part_acc, float* __restrict__ part_ml, int n_q_heads,
+                   int n_kv_heads, int page_size, float scale_log2, int window, int n_splits) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  bf16* sQ = reinterpret_cast<bf16*>(smem_raw);          // [16][STRIDE]
+  bf16* sKV = sQ + 16 * STRIDE;                          // 2 stages x (K, V) x [KV_TILE][STRIDE]
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int group = n_q_heads / n_kv_heads;
+  const int chunks_per_kv = (group + 15) / 16;
+  const int kvh = blockIdx.y / chunks_per_kv;
+  const int head0 = kvh * group + (blockIdx.y % chunks_per_kv) * 16;
+  int n_heads_here = kvh * group + group - head0;
+  if (n_heads_here > 16) n_heads_here = 16;
+  const int seq = single_seqs[blockIdx.x];
+  const int tok = cu_q[seq];
+  const int pos = positions[tok];
+  const int k_lo_all = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  const int* table = block_table + (long long)seq * table_stride;
+
+  // this block's share of the key tiles [tile_a, tile_b)
+  const int tile_first = k_lo_all / KV_TILE, tile_end = pos / KV_TILE + 1;
+  const int n_tiles = tile_end - tile_first;
+  const int per = (n_tiles + n_splits - 1) / n_splits;
+  const int tile_a = tile_first + blockIdx.z * per;
+  int tile_b = tile_a + per;
+  if (tile_b > tile_end) tile_b = tile_end;
+
+  float o[D / 8][4];
+#pragma unroll
+  for (int dt = 0; dt < D / 8; ++dt)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[dt][e] = 0.0f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
+
+  if (tile_a < tile_b) {
+    if (tid < 16 * 2) {  // Q rows: one per query head of the chunk, the rest zero
+      const int row = tid >> 1, half = tid & 1;
+      const bool valid = row < n_heads_here;
+      const bf16* src = q + (long long)tok * q_stride + (long long)(head0 + (valid ? row : 0)) * D;
+#pragma unroll
+      for (int c = 0; c < CHUNKS / 2; ++c) {
+        const int chunk = half * (CHUNKS / 2) + c;
+        cp_async16(sQ + row * STRIDE + chunk * 8, src + chunk * 8, valid);
+      }
+    }
+    load_kv_tile(sKV, sKV + KV_TILE * STRIDE, pool, table, tile_a * KV_TILE, k_lo_all, pos, kvh,
+                 n_kv_heads, page_size);
+    cp_async_commit();
+    for (int tile = tile_a; tile < tile_b; ++tile) {
+      const int stage = (tile - tile_a) & 1;
+      bf16* sK = sKV + stage * 2 * KV_TILE * STRIDE;
+      bf16* sV = sK + KV_TILE * STRIDE;
+      if (tile + 1 < tile_b) {
+        bf16* nK = sKV + (stage ^ 1) * 2 * KV_TILE * STRIDE;
+        load_kv_tile(nK, nK + KV_TILE * STRIDE, pool, table, (tile + 1) * KV_TILE, k_lo_all, pos,
+                     kvh, n_kv_heads, page_size);
+        cp_async_commit();
+        cp_async_wait<1>();
+      } else {
+        cp_async_wait<0>();
+      }
+      __syncthreads();
+      const int key0 = tile * KV_TILE + warp * 16;
+      if (key0 <= pos && key0 + 15 >= k_lo_all) {
+        float s[2][4];
+        qk_tile<2>(s, sQ, sK + warp * 16 * STRIDE);
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int j = key0 + nt * 8 + (lane & 3) * 2 + (e & 1);
+            const bool ok = j <= pos && j >= k_lo_all;
+            s[nt][e] = ok ? s[nt][e] * scale_log2 : -INFINITY;
+          }
+        softmax_update<2>(s, m, l, o);
+        pv_tile<2>(o, s, sV + warp * 16 * STRIDE);
+      }
+      __syncthreads();
+    }
+  }
+
+  // ---- merge the four warps (each saw different keys) in shared memory
+  // layout: wm[4][16], wl[4][16], wacc[4][16][D] floats, over the K/V stages
+  float* wm = reinterpret_cast<float*>(sKV);
+  float* wl = wm + 4 * 16;
+  float* wacc = wl + 4 * 16;
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    float lt = l[r];
+    lt += __shfl_xor_sync(0xffffffffu, lt, 1);
+    lt += __shfl_xor_sync(0xffffffffu, lt, 2);
+    const int row = (lane >> 2) + 8 * r;
+    if ((lane & 3) == 0) {
+      wm[warp * 16 + row] = m[r];
+      wl[warp * 16 + row] = lt;
+    }
+#pragma unroll
+    for (int dt = 0; dt < D / 8; ++dt) {
+      float* dst = wacc + ((warp * 16 + row) * D) + dt * 8 + (lane & 3) * 2;
+      dst[0] = o[dt][2 * r];
+      dst[1] = o[dt][2 * r + 1];
+    }
+  }
+  __syncthreads();
+  for (int idx = tid; idx < n_heads_here * D; idx += THREADS) {
+    const int row = idx / D, d = idx - row * D;
+    float mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) mm = fmaxf(mm, wm[w * 16 + row]);
+    float acc = 0.0f, lsum = 0.0f;
+    if (mm != -INFINITY) {
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const float f = exp2f(wm[w * 16 + row] - mm);
+        acc += f * wacc[(w * 16 + row) * D + d];
+        lsum += f * wl[w * 16 + row];
+      }
+    }
+    const int head = head0 + row;
+    if (n_splits == 1) {
+      out[(long long)tok * out_stride + (long long)head * D + d] = from_f32<bf16>(acc / lsum);
+    } else {
+      const long long p = ((long long)blockIdx.x * n_q_heads + head) * n_splits + blockIdx.z;
+      part_acc[p * D + d] = acc;
+      if (d == 0) {
+        part_ml[p * 2] = mm;
+        part_ml[p * 2 + 1] = lsum;
+      }
+    }
+  }
+}
+
+// grid (sequences with one token, query heads); joins the splits' partial results.
+__global__ void attn_merge_kernel(const float* __restrict__ part_acc,
+                                  const float* __restrict__ part_ml,
+                                  const int* __restrict__ cu_q,
+                                  const int* __restrict__ single_seqs, bf16* __restrict__ out,
+                                  int out_stride, int n_q_heads, int n_splits) {
+  const int head = blockIdx.y;
+  const int tok = cu_q[single_seqs[blockIdx.x]];
+  const long long base = ((long long)blockIdx.x * n_q_heads + head) * n_splits;
+  float mm = -INFINITY;
+  for (int z = 0; z < n_splits; ++z) mm = fmaxf(mm, part_ml[(base + z) * 2]);
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    float acc = 0.0f, lsum = 0.0f;
+    for (int z = 0; z < n_splits; ++z) {
+      const float mz = part_ml[(base + z) * 2];
+      if (mz == -INFINITY) continue;  // a split with no keys
+      const float f = exp2f(mz - mm);
+      acc += f * part_acc[(base + z) * D + d];
+      lsum += f * part_ml[(base + z) * 2 + 1];
+    }
+    out[(long long)tok * out_stride + (long long)head * D + d] = from_f32<bf16>(acc / lsum);
+  }
+}
+
+constexpr size_t PREFILL_SMEM = (size_t)(Q_TILE + 4 * KV_TILE) * STRIDE * sizeof(bf16);
+constexpr size_t DECODE_KV_SMEM = (size_t)4 * KV_TILE * STRIDE * sizeof(bf16);
+constexpr size_t DECODE_MERGE_SMEM = (size_t)(2 * 4 * 16 + 4 * 16 * D) * sizeof(float);
+constexpr size_t DECODE_SMEM =
+    (size_t)16 * STRIDE * sizeof(bf16) +
+    (DECODE_KV_SMEM > DECODE_MERGE_SMEM ? DECODE_KV_SMEM : DECODE_MERGE_SMEM);
+
+}  // namespace si
+
+SI_API int si_attn_head_dim() { return si::D; }
+
+// Attention for the 64-query tiles listed in tile_seq/tile_start.
+SI_API int si_attn_prefill(const void* q, int q_stride, const void* pool, const int* block_table,
+                           int table_stride, const int* cu_q, const int* positions,
+                           const int* tile_seq, const int* tile_start, int n_tiles, void* out,
+                           int out_stride, int n_q_heads, int n_kv_heads, int page_size,
+                           float scale, int window, cudaStream_t stream) {
+  if (!q || !pool || !block_table || !cu_q || !positions || !tile_seq || !tile_start || !out)
+    return SI_ERR_ARG;
+  if (n_tiles < 0 || n_q_heads <= 0 || n_kv_heads <= 0 || n_q_heads % n_kv_heads != 0 ||
+      page_size <= 0 || table_stride <= 0 || q_stride % 8 != 0 || out_stride % 2 != 0)
+    return SI_ERR_ARG;
+  if (n_q_heads > 65535) return SI_ERR_TOO_LARGE;
+  if (n_tiles == 0) return SI_OK;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(si::attn_prefill_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)si::PREFILL_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  dim3 grid(n_tiles, n_q_heads);
+  si::attn_prefill_kernel<<<grid, si::THREADS, si::PREFILL_SMEM, stream>>>(
+      (const si::bf16*)q, q_stride, (const si::bf16*)pool, block_table, table_stride, cu_q,
+      positions, tile_seq, tile_start, (si::bf16*)out, out_stride, n_q_heads, n_kv_heads,
+      page_size, scale * si::LOG2E, window);
+  SI_LAUNCH_CHECK();
+  return SI_OK;
+}
+
+// Floats of scratch the decode path needs: part_acc then part_ml.
+SI_API long long si_attn_decode_scratch_floats(int n_single, int n_q_heads, int n_splits) {
+  if (n_splits <= 1) return 0;
+  return (long long)n_single * n_q_heads * n_splits * (si::D + 2);
+}
+
+// Attention for the sequences listed in single_seqs (one token each).
+// scratch: si_attn_decode_scratch_floats(...) floats, may be null when n_splits == 1.
+SI_API int si_attn_decode(const void* q, int q_stride, const void* pool, const int* block_table,
+                          int table_stride, const int* cu_q, const int* positions,
+                          const int* single_seqs, int n_single, void* out, int out_stride,
+                          float* scratch, int n_q_heads, int n_kv_heads, int page_size,
+                          float scale, int window, int n_splits, cudaStream_t stream) {
+  if (!q || !pool || !block_table || !cu_q || !positions || !single_seqs || !out)
+    return SI_ERR_ARG;
+  if (n_single < 0 || n_q_heads <= 0 || n_kv_heads <= 0 || n_q_heads % n_kv_heads != 0 ||
+      page_size <= 0 || table_stride <= 0 || q_stride % 8 != 0 || n_splits < 1)
+    return SI_ERR_ARG;
+  if (n_splits > 1 && !scratch) return SI_ERR_ARG;
+  const int group = n_q_heads / n_kv_heads;
+  const int grid_y = n_kv_heads * ((group + 15) / 16);
+  if (grid_y > 65535 || n_splits > 65535 || n_q_heads > 65535) return SI_ERR_TOO_LARGE;
+  if (n_single == 0) return SI_OK;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(si::attn_decode_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)si::DECODE_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  float* part_acc = scratch;
+  float* part_ml = scratch ? scratch + (long long)n_single * n_q_heads * n_splits * si::D : nullptr;
+  dim3 grid(n_single, grid_y, n_splits);
+  si::attn_decode_kernel<<<grid, si::THREADS, si::DECODE_SMEM, stream>>>(
+      (const si::bf16*)q, q_stride, (const si::bf16*)pool, block_table, table_stride, cu_q,
+      positions, single_seqs, (si::bf16*)out, out_stride, part_acc, part_ml, n_q_heads, n_kv_heads,
+      page_size, scale * si::LOG2E, window, n_splits);
+  SI_LAUNCH_CHECK();
+  if (n_splits > 1) {
+    dim3 mgrid(n_single, n_q_heads);
+    si::attn_merge_kernel<<<mgrid, si::D >= 128 ? 128 : 64, 0, stream>>>(
+        part_acc, part_ml, cu_q, single_seqs, (si::bf16*)out, out_stride, n_q_heads, n_splits);
+    SI_LAUNCH_CHECK();
+  }
+  return SI_OK;
+}

@@ -98,6 +98,7 @@ class StepContext:
     n_tiles: int
     max_kv_len: int
     max_q_len: int
+    max_seqs: int
     ws: Workspace
     # host copies for parts that plan on the host
     q_lens: list[int] = field(default_factory=list)
@@ -251,5 +252,5 @@ class BatchBuilder:
             single_seqs=self._d("single_seqs", n_single), n_single=n_single,
             tile_seq=self._d("tile_seq", n_tiles), tile_start=self._d("tile_start", n_tiles),
             n_tiles=n_tiles, max_kv_len=max(kv_lens) if kv_lens else 0,
-            max_q_len=max(q_lens) if q_lens else 0, ws=ws, q_lens=q_lens, kv_lens=kv_lens,
+            max_q_len=max(q_lens) if q_lens else 0, max_seqs=self.max_seqs, ws=ws, q_lens=q_lens, kv_lens=kv_lens,
         )

@@ -218,6 +218,19 @@ def attention_generic(q: torch.Tensor, pool: torch.Tensor, block_table: torch.Te
     return out
 
 
+MAX_KV_SPLITS = 32
+_TARGET_BLOCKS = 2 * 148  # two resident blocks on each of the 148 SMs
+
+
+def plan_kv_splits(n_single: int, num_q_heads: int, num_kv_heads: int, max_kv_len: int) -> int:
+    """How many blocks share the keys of one (sequence, kv head) in the decode kernel."""
+    group = num_q_heads // num_kv_heads
+    base = max(1, n_single * num_kv_heads * ((group + 15) // 16))
+    tiles = max(1, (max_kv_len + 63) // 64)
+    want = (_TARGET_BLOCKS + base - 1) // base
+    return max(1, min(MAX_KV_SPLITS, tiles, want))
+
+
 def paged_attention(q: torch.Tensor, pool: torch.Tensor, ctx, group: int, out: torch.Tensor,
                     num_q_heads: int, num_kv_heads: int, head_dim: int, scale: float,
                     window: int | None) -> torch.Tensor:
@@ -225,10 +238,41 @@ def paged_attention(q: torch.Tensor, pool: torch.Tensor, ctx, group: int, out: t
 
     ``ctx`` is the step's ``StepContext``.  float32: the generic kernel for every
     token.  bfloat16: tensor-core kernels, one for sequences that bring a single
-    token (split over the keys) and one for longer portions (64-query tiles).
+    token (keys split over blocks, partial results joined through scratch memory)
+    and one for longer portions (64-query tiles).
     """
-    return attention_generic(q, pool, ctx.block_tables[group], ctx.tok_seq, ctx.positions, out,
-                             num_q_heads, num_kv_heads, head_dim, scale, window)
+    table = ctx.block_tables[group]
+    if q.dtype == torch.float32:
+        return attention_generic(q, pool, table, ctx.tok_seq, ctx.positions, out, num_q_heads,
+                                 num_kv_heads, head_dim, scale, window)
+    _dev(pool, table, out)
+    if not q.is_cuda or q.stride(1) != 1 or q.dtype != torch.bfloat16:
+        raise KernelError("attention: q must be a bfloat16 CUDA tensor with unit inner stride")
+    page_size = pool.shape[3]
+    if tuple(pool.shape[1:]) != (2, num_kv_heads, page_size, head_dim) or \
+            pool.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("attention: pool/out shape or dtype does not fit")
+    lib = attention_library(head_dim)
+    win = int(window or 0)
+    if ctx.n_tiles:
+        _check(lib.si_attn_prefill(
+            _p(q), q.stride(0), _p(pool), _p(table), table.stride(0), _p(ctx.cu_q),
+            _p(ctx.positions), _p(ctx.tile_seq), _p(ctx.tile_start), ctx.n_tiles, _p(out),
+            out.stride(0), num_q_heads, num_kv_heads, page_size, _c_float(scale), win, _stream()),
+            "attn_prefill")
+    if ctx.n_single:
+        n_splits = plan_kv_splits(ctx.n_single, num_q_heads, num_kv_heads, ctx.max_kv_len)
+        scratch = None
+        if n_splits > 1:
+            scratch = ctx.ws.get("attn.split",
+                                 (ctx.n_single, num_q_heads * MAX_KV_SPLITS * (head_dim + 2)),
+                                 torch.float32, row_cap=ctx.max_seqs)
+        _check(lib.si_attn_decode(
+            _p(q), q.stride(0), _p(pool), _p(table), table.stride(0), _p(ctx.cu_q),
+            _p(ctx.positions), _p(ctx.single_seqs), ctx.n_single, _p(out), out.stride(0),
+            _p(scratch), num_q_heads, num_kv_heads, page_size, _c_float(scale), win, n_splits,
+            _stream()), "attn_decode")
+    return out
 
 
 # ----------------------------------------------------------------- sampling
@@ -254,4 +298,4 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
 
 
 __all__ = ["KernelError", "KernelBuildError", "embed_gather", "rmsnorm", "swiglu", "linear",
-           "rope_kv_store", "attention_generic", "paged_attention", "sample", "core", "attention_library"]
+           "rope_kv_store", "attention_generic", "paged_attention", "plan_kv_splits", "sample", "core", "attention_library"]
