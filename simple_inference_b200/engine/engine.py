@@ -242,7 +242,7 @@ class InferenceEngine:
                 yield out[req.id]
 
     def generate_with_stats(self, prompt_tokens: list[int], max_new_tokens: int = 256,
-                            **sampling: Any) -> tuple[list[int], dict[str, float]]:
+                            on_token=None, **sampling: Any) -> tuple[list[int], dict[str, float]]:
         """Tokens of one request and the reference's timing record (``generate.py:132-237``)."""
         cuda = self.rt.device.type == "cuda"
         if cuda:
@@ -254,6 +254,8 @@ class InferenceEngine:
         for tok in self.generate(prompt_tokens, max_new_tokens, **sampling):
             out.append(tok)
             stamps.append(time.perf_counter())
+            if on_token is not None:
+                on_token(tok)
         wall = time.perf_counter() - start
         ttft = (stamps[0] - start) if stamps else wall
         gaps = [b - a for a, b in zip(stamps, stamps[1:])]
