@@ -1,0 +1,332 @@
+#!/usr/bin/env python3
+"""Headline benchmark: decode tokens/s of the Llama 3.2 3B shape on one B200.
+
+Contract: ``python bench.py --gpus N --steps K --warmup W`` prints ONE JSON line.
+A step is one decode step of a batch of 8 requests at context 2,048 (the decode
+workload of the reference's headline configuration), bfloat16, random weights,
+synthetic token ids.  ``value`` is decoded tokens per second timed on the device
+with CUDA events; ``e2e`` is the same through ``InferenceEngine.step()`` with
+host token ids in and sampled ids out every step.  The line also carries the
+prefill of 2,048 tokens, the decode roofline (weights + live cache bytes over
+the step time against the measured copy bandwidth) and decode at batch 1 and 64.
+This engine runs on one GPU: for N > 1 it says so and exits with 2.
+
+``--impl reference`` would run the unmodified reference from ``baseline/_ref``;
+the reference is a flat folder of modules without packaging metadata that pip
+refuses to install, so that arm prints its ``unavailable`` line.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+LLAMA_3_2_3B = {
+    "architectures": ["LlamaForCausalLM"],
+    "num_hidden_layers": 28, "hidden_size": 3072, "num_attention_heads": 24,
+    "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 8192, "vocab_size": 128256,
+    "rope_theta": 500000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 32.0, "low_freq_factor": 1.0,
+                     "high_freq_factor": 4.0, "original_max_position_embeddings": 8192},
+    "rms_norm_eps": 1e-5, "tie_word_embeddings": True, "max_position_embeddings": 131072,
+    "torch_dtype": "bfloat16",
+}
+MAX_CONTEXT = 4096
+DECODE_CONTEXT = 2048
+PREFILL_TOKENS = 2048
+PAGE_SIZE = 16
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+
+
+def peaks() -> tuple[dict, str]:
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.is_file():
+        try:
+            raw = json.loads(path.read_text())
+            out = dict(FALLBACK_PEAKS)
+            for k in out:
+                if isinstance(raw.get(k), (int, float)):
+                    out[k] = float(raw[k])
+            return out, "measured"
+        except Exception:
+            pass
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region is timed."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.samples: list[list[str]] = []
+        self.proc = None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) == 6:
+                self.samples.append(parts)
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self) -> dict:
+        mhz = sorted(int(s[0]) for s in self.samples if s[0].isdigit())
+        mx = [int(s[1]) for s in self.samples if s[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(s[2 + i] == "Active" for s in self.samples)]
+        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(self.samples)}
+
+
+def matmul_params(cfg) -> tuple[int, int]:
+    """(elements of the layers' matrices, elements of the output head)."""
+    h, d = cfg.hidden_size, cfg.head_dim
+    per_layer = (cfg.num_attention_heads + 2 * cfg.num_key_value_heads) * d * h \
+        + h * cfg.num_attention_heads * d + 3 * h * cfg.intermediate_size
+    return per_layer * cfg.num_hidden_layers, cfg.vocab_size * h
+
+
+def kv_bytes_per_token(cfg, elt=2) -> int:
+    return 2 * cfg.num_key_value_heads * cfg.head_dim * elt * cfg.num_hidden_layers
+
+
+def build_runner(model, batch, layers_note=None):
+    import torch
+    from simple_inference_b200.cache import CacheManager, pages_for
+    from simple_inference_b200.engine import ModelRunner
+    rt = model.rt
+    pages = batch * pages_for(MAX_CONTEXT, PAGE_SIZE)
+    cache = CacheManager(model.cache_specs(), PAGE_SIZE, pages, batch, max(PREFILL_TOKENS, batch),
+                         dtype=rt.dtype, device=rt.device)
+    runner = ModelRunner(model, cache, rt, max(PREFILL_TOKENS, batch), batch, MAX_CONTEXT,
+                         cuda_graphs=True)
+    return cache, runner
+
+
+def fill_context(cache, runner, batch, vocab, seed):
+    """Admit ``batch`` requests and run their first DECODE_CONTEXT - 1 tokens."""
+    import torch
+    from simple_inference_b200.engine import StepEntry
+    g = torch.Generator().manual_seed(seed)
+    for b in range(batch):
+        cache.admit(b, MAX_CONTEXT)
+        ids = torch.randint(0, vocab, (DECODE_CONTEXT - 1,), generator=g).tolist()
+        runner.step([StepEntry(b, ids, [])])
+    torch.cuda.synchronize()
+
+
+def time_decode(model, cfg, batch, steps, warmup, sample_clocks=False):
+    """Device-timed decode: per step one metadata copy, the captured graph, the sampling kernel."""
+    import torch
+    from simple_inference_b200 import ops
+    from simple_inference_b200.engine import StepEntry
+    from simple_inference_b200.sampling import Sampler, SamplingParams
+    cache, runner = build_runner(model, batch)
+    fill_context(cache, runner, batch, cfg.vocab_size, seed=batch)
+    sampler = Sampler(model.rt.device, batch)
+    g = torch.Generator().manual_seed(1000 + batch)
+    feed = torch.randint(0, cfg.vocab_size, (steps + warmup, batch), generator=g).tolist()
+    greedy = [(SamplingParams(), 0, 0)] * batch
+
+    def one(i):
+        logits = runner.step([StepEntry(b, [feed[i][b]], [0]) for b in range(batch)])
+        # sampling stays on the device here: no read-back inside the device-timed region
+        d = sampler._dev
+        ops.sample(logits, sampler._field(d, 0, batch).view(torch.float32), sampler._field(d, 1, batch),
+                   sampler._field(d, 2, batch).view(torch.float32), sampler._field(d, 3, batch),
+                   sampler._field(d, 4, batch), sampler._field(d, 5, batch), sampler._out[:batch])
+
+    sampler.sample(runner.step([StepEntry(b, [1], [0]) for b in range(batch)]), greedy)  # sets params
+    for i in range(warmup):
+        one(i)
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    k0, r0 = ops.launch_count, runner.replayed_kernels
+    clocks = ClockSampler() if sample_clocks else None
+    if clocks:
+        clocks.__enter__()
+    torch.cuda.synchronize()
+    start.record()
+    for i in range(warmup, warmup + steps):
+        one(i)
+    end.record()
+    torch.cuda.synchronize()
+    if clocks:
+        clocks.__exit__(None, None, None)
+    ms = start.elapsed_time(end) / steps
+    launches = (ops.launch_count - k0) + (runner.replayed_kernels - r0)
+    ctx_mean = DECODE_CONTEXT + 1 + warmup + (steps - 1) / 2
+    del runner, cache
+    torch.cuda.empty_cache()
+    return ms, launches, ctx_mean, (clocks.summary() if clocks else None)
+
+
+def time_e2e(model, cfg, batch, steps, warmup):
+    """The same decode through InferenceEngine.step(): host ids in, sampled ids out, every step."""
+    import torch
+    from simple_inference_b200 import InferenceEngine
+    eng = InferenceEngine(model, max_running=batch, max_seq_len=MAX_CONTEXT, block_size=PAGE_SIZE,
+                          eos_id=-1, temperature=0.0, max_tokens_per_step=PREFILL_TOKENS,
+                          use_cuda_graphs=True, warmup=False)
+    g = torch.Generator().manual_seed(7)
+    for _ in range(batch):
+        eng.add_request(torch.randint(0, cfg.vocab_size, (DECODE_CONTEXT,), generator=g).tolist(),
+                        steps + warmup + 8)
+    while any(r.prefilled < r.prompt_len for r in eng.scheduler.running) or eng.scheduler.waiting:
+        eng.step()
+    for _ in range(warmup):
+        eng.step()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        out = eng.step()
+        assert len(out) == batch
+    torch.cuda.synchronize()
+    dt = (time.perf_counter() - t0) / steps
+    h2d = eng.runner.builder.total * 4 + eng.sampler._host.numel() * 4
+    d2h = batch * 4
+    eng.reset()
+    del eng
+    torch.cuda.empty_cache()
+    return dt * 1e3, h2d, d2h
+
+
+def time_prefill(model, cfg, reps=5):
+    import torch
+    from simple_inference_b200.engine import StepEntry
+    cache, runner = build_runner(model, 1)
+    g = torch.Generator().manual_seed(3)
+    ids = torch.randint(0, cfg.vocab_size, (PREFILL_TOKENS,), generator=g).tolist()
+    times = []
+    for i in range(reps + 2):
+        cache.admit(i, MAX_CONTEXT)
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        runner.step([StepEntry(i, ids, [PREFILL_TOKENS - 1])])
+        end.record()
+        torch.cuda.synchronize()
+        times.append(start.elapsed_time(end))
+        cache.release(i)
+    del runner, cache
+    torch.cuda.empty_cache()
+    return sorted(times[2:])[len(times[2:]) // 2]
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=None, help="run fewer layers (named in config)")
+    ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
+    args = ap.parse_args()
+
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "pip cannot install the reference offline: it is a flat folder of modules "
+                          "with no package metadata (setuptools: multiple top-level packages), so "
+                          "baseline/_ref is empty"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not built")
+        return 2
+    warmup = max(args.warmup, 3)
+
+    import torch
+    from simple_inference_b200.models.load import random_model
+    if not torch.cuda.is_available():
+        print("bench.py: no CUDA device")
+        return 1
+    pk, pk_src = peaks()
+    config = dict(LLAMA_3_2_3B)
+    full_layers = config["num_hidden_layers"]
+    if args.layers:
+        config["num_hidden_layers"] = args.layers
+    cfg, model = random_model(config, seed=0, dtype="bfloat16", device="cuda:0")
+    layer_params, head_params = matmul_params(cfg)
+    weight_bytes = 2 * (layer_params + head_params)
+
+    ms, launches, ctx_mean, clocks = time_decode(model, cfg, args.batch, args.steps, warmup, True)
+    step_bytes = weight_bytes + args.batch * ctx_mean * kv_bytes_per_token(cfg)
+    achieved = step_bytes / (ms * 1e-3) / 1e9
+    e2e_ms, h2d, d2h = time_e2e(model, cfg, args.batch, args.steps, warmup)
+
+    pre_ms = time_prefill(model, cfg)
+    T, d = PREFILL_TOKENS, cfg.head_dim
+    flops = 2 * T * layer_params + 2 * head_params \
+        + cfg.num_hidden_layers * 2 * cfg.num_attention_heads * d * T * (T + 1)  # QK^T and PV, causal
+    pre_frac = flops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12)
+
+    points = {}
+    if not args.no_points:
+        for b in (1, 64):
+            pms, _, _, _ = time_decode(model, cfg, b, max(10, args.steps // 2), warmup)
+            points[f"decode_b{b}"] = round(b / (pms * 1e-3), 1)
+
+    line = {
+        "metric": "decode tok/s, Llama 3.2 3B shape, batch 8, context 2048 (1 GPU)",
+        "value": round(args.batch / (ms * 1e-3), 1), "unit": "tokens/s", "n_gpus": 1,
+        "steps": args.steps, "warmup": warmup, "ms_per_step": round(ms, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: random weights N(0,0.02) seed 0, uniform-random token ids",
+        "impl": "ours",
+        "config": {
+            "model": "llama-3.2-3b-shape", "layers": cfg.num_hidden_layers,
+            "layers_of_full_model": full_layers, "hidden": cfg.hidden_size,
+            "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
+            "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size,
+            "vocab": cfg.vocab_size, "global_batch": args.batch, "seq_len": DECODE_CONTEXT,
+            "max_context": MAX_CONTEXT, "page_size": PAGE_SIZE, "prefill_tokens": PREFILL_TOKENS,
+            "parallelism": "single-gpu", "cuda_graph": True,
+            "l2": "inputs larger than L2: every step streams the weights (GBs) once",
+            "peaks": pk_src,
+        },
+        "e2e": {"value": round(args.batch / (e2e_ms * 1e-3), 1), "unit": "tokens/s",
+                "ms_per_step": round(e2e_ms, 4), "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h},
+        "gpu_launches": launches,
+        "prefill": {"value": round(T / (pre_ms * 1e-3), 1), "tokens": T, "ms": round(pre_ms, 3),
+                    "frac": round(pre_frac, 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"],
+                     "unit": "GB/s", "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points,
+        "clocks": clocks,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -53,6 +53,8 @@ class ModelRunner:
         self.layer_caches = cache.layer_caches()
         self.cuda_graphs = cuda_graphs and rt.device.type == "cuda"
         self._graphs: dict[int, tuple[torch.cuda.CUDAGraph, torch.Tensor]] = {}
+        self._graph_kernels: dict[int, int] = {}   # bucket -> kernels of this package in its graph
+        self.replayed_kernels = 0                  # kernels launched through graph replays so far
         self._buckets = decode_buckets(max_seqs)
         self.last_context: StepContext | None = None
 
@@ -107,6 +109,7 @@ class ModelRunner:
             self._capture(bucket, ctx)
         graph, logits = self._graphs[bucket]
         graph.replay()
+        self.replayed_kernels += self._graph_kernels[bucket]
         return logits[:len(entries)]
 
     def _capture(self, bucket: int, ctx: StepContext) -> None:
@@ -123,9 +126,13 @@ class ModelRunner:
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
         self.ws.freeze()
+        from .. import ops
         graph = torch.cuda.CUDAGraph()
+        before = ops.launch_count
         with torch.cuda.graph(graph):
             logits = self.model.forward(ctx, self.layer_caches)
+        self._graph_kernels[bucket] = ops.launch_count - before
+        ops.launch_count = before  # recorded, not run
         self._graphs[bucket] = (graph, logits)
 
     def capture_all(self) -> None:

@@ -54,8 +54,13 @@ def attention_library(head_dim: int) -> ctypes.CDLL:
     return load_library(f"si_attn_d{head_dim}", ["attention_mma.cu"], [f"-DSI_HEAD_DIM={head_dim}"])
 
 
-def _check(code: int, what: str) -> None:
+launch_count = 0  # kernels of this package launched so far (a graph replay is counted by its owner)
+
+
+def _check(code: int, what: str, kernels: int = 1) -> None:
+    global launch_count
     if code == 0:
+        launch_count += kernels
         return
     if code < 0:
         raise KernelError(f"{what}: refused, {_ERRORS.get(code, code)}")
@@ -271,7 +276,7 @@ def paged_attention(q: torch.Tensor, pool: torch.Tensor, ctx, group: int, out: t
             _p(q), q.stride(0), _p(pool), _p(table), table.stride(0), _p(ctx.cu_q),
             _p(ctx.positions), _p(ctx.single_seqs), ctx.n_single, _p(out), out.stride(0),
             _p(scratch), num_q_heads, num_kv_heads, page_size, _c_float(scale), win, n_splits,
-            _stream()), "attn_decode")
+            _stream()), "attn_decode", kernels=2 if n_splits > 1 else 1)
     return out
 
 
