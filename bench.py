@@ -119,6 +119,9 @@ def kv_bytes_per_token(cfg, elt=2) -> int:
     return 2 * cfg.num_key_value_heads * cfg.head_dim * elt * cfg.num_hidden_layers
 
 
+EAGER = False  # --eager: no CUDA graphs, so that a profiler sees every kernel as its own launch
+
+
 def build_runner(model, batch, layers_note=None):
     import torch
     from simple_inference_b200.cache import CacheManager, pages_for
@@ -128,7 +131,7 @@ def build_runner(model, batch, layers_note=None):
     cache = CacheManager(model.cache_specs(), PAGE_SIZE, pages, batch, max(PREFILL_TOKENS, batch),
                          dtype=rt.dtype, device=rt.device)
     runner = ModelRunner(model, cache, rt, max(PREFILL_TOKENS, batch), batch, MAX_CONTEXT,
-                         cuda_graphs=True)
+                         cuda_graphs=not EAGER)
     return cache, runner
 
 
@@ -175,11 +178,13 @@ def time_decode(model, cfg, batch, steps, warmup, sample_clocks=False):
     if clocks:
         clocks.__enter__()
     torch.cuda.synchronize()
+    torch.cuda.profiler.start()  # a profiler started with --profile-from-start off sees only this
     start.record()
     for i in range(warmup, warmup + steps):
         one(i)
     end.record()
     torch.cuda.synchronize()
+    torch.cuda.profiler.stop()
     if clocks:
         clocks.__exit__(None, None, None)
     ms = start.elapsed_time(end) / steps
@@ -200,7 +205,7 @@ def time_e2e(model, cfg, batch, steps, warmup):
     g = torch.Generator().manual_seed(7)
     for _ in range(batch):
         eng.add_request(torch.randint(0, cfg.vocab_size, (DECODE_CONTEXT,), generator=g).tolist(),
-                        steps + warmup + 8)
+                        steps + warmup + 4 * batch + 16)  # earlier requests decode while later ones prefill
     while any(r.prefilled < r.prompt_len for r in eng.scheduler.running) or eng.scheduler.waiting:
         eng.step()
     for _ in range(warmup):
@@ -231,10 +236,14 @@ def time_prefill(model, cfg, reps=5):
         cache.admit(i, MAX_CONTEXT)
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         torch.cuda.synchronize()
+        if i == reps + 1:
+            torch.cuda.profiler.start()
         start.record()
         runner.step([StepEntry(i, ids, [PREFILL_TOKENS - 1])])
         end.record()
         torch.cuda.synchronize()
+        if i == reps + 1:
+            torch.cuda.profiler.stop()
         times.append(start.elapsed_time(end))
         cache.release(i)
     del runner, cache
@@ -251,7 +260,12 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers (named in config)")
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
+    ap.add_argument("--only", choices=["decode", "prefill"],
+                    help="run one part and print a short record (for profiling; not the contract line)")
+    ap.add_argument("--eager", action="store_true", help="no CUDA graphs (for kernel-level profiles)")
     args = ap.parse_args()
+    global EAGER
+    EAGER = args.eager
 
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -277,6 +291,17 @@ def main() -> int:
     cfg, model = random_model(config, seed=0, dtype="bfloat16", device="cuda:0")
     layer_params, head_params = matmul_params(cfg)
     weight_bytes = 2 * (layer_params + head_params)
+
+    if args.only == "decode":
+        ms, launches, _, _ = time_decode(model, cfg, args.batch, args.steps, args.warmup)
+        print(json.dumps({"only": "decode", "batch": args.batch, "layers": cfg.num_hidden_layers,
+                          "eager": EAGER, "ms_per_step": round(ms, 4), "launches": launches}))
+        return 0
+    if args.only == "prefill":
+        pre_ms = time_prefill(model, cfg, reps=max(1, args.steps))
+        print(json.dumps({"only": "prefill", "tokens": PREFILL_TOKENS,
+                          "layers": cfg.num_hidden_layers, "ms": round(pre_ms, 3)}))
+        return 0
 
     ms, launches, ctx_mean, clocks = time_decode(model, cfg, args.batch, args.steps, warmup, True)
     step_bytes = weight_bytes + args.batch * ctx_mean * kv_bytes_per_token(cfg)
