@@ -1,0 +1,261 @@
+"""Each CUDA kernel alone against its plain torch twin, at sizes other than the engine's."""
+
+import math
+import types
+
+import pytest
+import torch
+
+from tests import plain_llama, twin_ops
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from simple_inference_b200 import ops as o
+    return o
+
+
+def dev():
+    return torch.device("cuda")
+
+
+def gen(seed):
+    return torch.Generator(device="cuda").manual_seed(seed)
+
+
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n,h", [(7, 120), (33, 3072), (3, 50), (1, 16400)])
+def test_embedding_rmsnorm_swiglu(ops, dt, n, h):
+    g = gen(1)
+    table = torch.randn(300, h, device=dev(), generator=g).to(dt)
+    ids = torch.randint(0, 300, (n,), device=dev(), dtype=torch.int32)
+    a, b = torch.empty(n, h, device=dev()), torch.empty(n, h, device=dev())
+    ops.embed_gather(table, ids, a)
+    twin_ops.embed_gather(table, ids, b)
+    assert torch.equal(a, b)
+
+    res = torch.randn(n, h, device=dev(), generator=g)
+    delta = torch.randn(n, h, device=dev(), generator=g).to(dt)
+    gain = 1 + 0.1 * torch.randn(h, device=dev(), generator=g)
+    tol = 2e-6 if dt == torch.float32 else 2e-2      # one bfloat16 ulp at magnitude ~4
+    for wdt in (torch.float32, torch.bfloat16):
+        o1, o2 = torch.empty(n, h, device=dev(), dtype=dt), torch.empty(n, h, device=dev(), dtype=dt)
+        r1, r2 = res.clone(), res.clone()
+        ops.rmsnorm(r1, gain.to(wdt), 1e-5, o1, delta=delta)
+        twin_ops.rmsnorm(r2, gain.to(wdt), 1e-5, o2, delta=delta)
+        assert torch.equal(r1, r2), "the residual add is exact in float32"
+        assert (o1.float() - o2.float()).abs().max() < tol
+    rows = torch.tensor([n - 1, 0, n // 2], device=dev(), dtype=torch.int32)
+    o1, o2 = torch.empty(3, h, device=dev(), dtype=dt), torch.empty(3, h, device=dev(), dtype=dt)
+    r1 = res.clone()
+    ops.rmsnorm(r1, gain, 3e-6, o1, delta=delta, rows=rows)
+    twin_ops.rmsnorm(res.clone(), gain, 3e-6, o2, delta=delta, rows=rows)
+    assert torch.equal(r1, res), "with rows given the residual is left alone"
+    assert (o1.float() - o2.float()).abs().max() < tol
+
+    gu = torch.randn(n, 2 * h, device=dev(), generator=g).to(dt)
+    o1, o2 = torch.empty(n, h, device=dev(), dtype=dt), torch.empty(n, h, device=dev(), dtype=dt)
+    ops.swiglu(gu, o1)
+    twin_ops.swiglu(gu, o2)
+    assert (o1.float() - o2.float()).abs().max() < tol
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 50, 33), (65, 130, 100), (200, 331, 120), (3, 128256, 64)])
+def test_float32_matrix_product_is_true_float32_and_row_invariant(ops, m, n, k):
+    g = gen(2)
+    a = torch.randn(m, k, device=dev(), generator=g)
+    w = torch.randn(n, k, device=dev(), generator=g)
+    out = torch.empty(m, n, device=dev())
+    ops.linear(a, w, out)
+    ref = a.double() @ w.double().T
+    # a TF32 product would be off by ~1e-3 * sqrt(k); float32 stays near 1e-6 * sqrt(k)
+    assert (out.double() - ref).abs().max() < 4e-6 * math.sqrt(k) * 4
+    one = torch.empty(1, n, device=dev())
+    ops.linear(a[m // 2:m // 2 + 1].contiguous(), w, one)
+    assert torch.equal(one[0], out[m // 2]), "a row's result does not depend on the other rows"
+
+
+def test_bfloat16_matrix_product_with_float32_output(ops):
+    g = gen(3)
+    a = torch.randn(5, 96, device=dev(), generator=g).bfloat16()
+    w = torch.randn(331, 96, device=dev(), generator=g).bfloat16()
+    out = torch.empty(5, 331, device=dev())
+    ops.linear(a, w, out)
+    assert (out - a.float() @ w.float().T).abs().max() < 1e-3
+
+
+def paged_case(lens_q, starts, ps, hq, hkv, d, dt, seed=0):
+    """A batch of sequences: q_len new tokens after `start` tokens already in the cache."""
+    g = gen(seed)
+    S, N = len(lens_q), sum(lens_q)
+    kv = [s + q for s, q in zip(starts, lens_q)]
+    maxp = max((x + ps - 1) // ps for x in kv)
+    P = sum((x + ps - 1) // ps for x in kv) + 2
+    perm = torch.randperm(P, generator=torch.Generator().manual_seed(seed)).tolist()
+    bt = torch.full((S, maxp), -1, dtype=torch.int32)
+    tok_seq, pos, slots, cu, single, tile_seq, tile_start = [], [], [], [0], [], [], []
+    pi = 0
+    for s in range(S):
+        for lp in range((kv[s] + ps - 1) // ps):
+            bt[s, lp] = perm[pi]
+            pi += 1
+        for p in range(starts[s], kv[s]):
+            tok_seq.append(s)
+            pos.append(p)
+            slots.append(int(bt[s, p // ps]) * ps + p % ps)
+        cu.append(cu[-1] + lens_q[s])
+        if lens_q[s] == 1:
+            single.append(s)
+        else:
+            for q0 in range(0, lens_q[s], 64):
+                tile_seq.append(s)
+                tile_start.append(q0)
+    from simple_inference_b200.engine.batch import Workspace
+    I = lambda x: torch.tensor(x, dtype=torch.int32, device=dev())  # noqa: E731
+    pool = torch.randn(P + 1, 2, hkv, ps, d, device=dev(), generator=g).to(dt)
+    qkv = torch.randn(N, (hq + 2 * hkv) * d, device=dev(), generator=g).to(dt)
+    ctx = types.SimpleNamespace(
+        block_tables=[bt.to(dev())], tok_seq=I(tok_seq), positions=I(pos), cu_q=I(cu),
+        kv_slots=[I(slots)], single_seqs=I(single), n_single=len(single), tile_seq=I(tile_seq),
+        tile_start=I(tile_start), n_tiles=len(tile_seq), max_kv_len=max(kv), max_seqs=S,
+        ws=Workspace(dev(), N))
+    return qkv, pool, ctx, N
+
+
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("hq,hkv,d,ps", [(4, 2, 16, 4), (6, 3, 48, 8), (3, 1, 32, 16),
+                                          (24, 8, 128, 16), (2, 2, 256, 2), (5, 5, 80, 3)])
+def test_rope_and_page_write(ops, dt, hq, hkv, d, ps):
+    qkv, pool, ctx, n = paged_case([37, 1, 300], [0, 90, 11], ps, hq, hkv, d, dt)
+    inv = plain_llama.rope_frequencies(d, 10000.0, None).to(dev())
+    pool.zero_()
+    pool2 = pool.clone()
+    q1, q2 = qkv.clone(), qkv.clone()
+    ops.rope_kv_store(q1, ctx.positions, inv, ctx.kv_slots[0], pool, hq, hkv, d, ps, True)
+    twin_ops.rope_kv_store(q2, ctx.positions, inv, ctx.kv_slots[0], pool2, hq, hkv, d, ps, True)
+    tol = 2e-6 if dt == torch.float32 else 4e-2
+    assert (q1.float() - q2.float()).abs().max() < tol
+    assert (pool.float() - pool2.float()).abs().max() < tol
+    assert torch.equal(pool[-1], pool2[-1]) and float(pool[-1].abs().sum()) == 0   # scratch untouched
+    q3 = qkv.clone()
+    before = pool.clone()
+    ops.rope_kv_store(q3, ctx.positions, inv, None, None, hq, hkv, d, ps, False)
+    assert torch.equal(q3[:, :hq * d], q1[:, :hq * d]) and torch.equal(pool, before)
+
+
+@pytest.mark.parametrize("hq,hkv,d,ps,window", [(4, 2, 16, 4, None), (6, 3, 48, 8, None),
+                                                 (3, 1, 32, 16, 7), (24, 8, 128, 16, None),
+                                                 (2, 2, 256, 2, None), (5, 5, 80, 3, 33)])
+def test_generic_attention_float32(ops, hq, hkv, d, ps, window):
+    qkv, pool, ctx, n = paged_case([37, 1, 300, 2], [0, 90, 11, 513], ps, hq, hkv, d, torch.float32)
+    o1, o2 = torch.empty(n, hq * d, device=dev()), torch.empty(n, hq * d, device=dev())
+    ops.attention_generic(qkv, pool, ctx.block_tables[0], ctx.tok_seq, ctx.positions, o1, hq, hkv,
+                          d, 1 / math.sqrt(d), window)
+    twin_ops.attention_generic(qkv, pool, ctx.block_tables[0], ctx.tok_seq, ctx.positions, o2, hq,
+                               hkv, d, 1 / math.sqrt(d), window)
+    assert (o1 - o2).abs().max() < 5e-6
+
+
+CASES = [
+    ("tile of 64", [64], [0], 16, 4, 2, 128, None, None),
+    ("ragged portions", [37, 200, 2], [0, 0, 5], 4, 4, 2, 16, None, None),
+    ("portions deep in a context", [130, 70], [33, 500], 16, 24, 8, 128, None, None),
+    ("head size 48, three groups", [100, 3], [0, 77], 8, 6, 3, 48, None, None),
+    ("window over a tile edge", [65], [100], 16, 3, 1, 32, 40, None),
+    ("head size 256, page of 2", [300], [0], 2, 2, 2, 256, None, None),
+    ("first token", [1], [0], 16, 4, 2, 128, None, None),
+    ("decode at three depths", [1, 1, 1], [5, 300, 63], 16, 24, 8, 128, None, None),
+    ("decode, one split", [1, 1], [2047, 64], 16, 24, 8, 128, None, 1),
+    ("decode, seven splits", [1, 1], [2047, 64], 16, 24, 8, 128, None, 7),
+    ("decode, more splits than tiles", [1, 1], [100, 3], 16, 24, 8, 128, None, 32),
+    ("decode, tiny heads", [1, 1, 1, 1], [0, 1, 100, 17], 4, 4, 2, 16, None, None),
+    ("decode with a window", [1, 1], [200, 30], 8, 6, 3, 48, 50, None),
+    ("twenty heads per group", [1], [500], 16, 40, 2, 64, None, None),
+    ("decode, head size 256", [1], [1000], 2, 2, 2, 256, None, None),
+    ("portions beside decode tokens", [1, 50, 1, 2, 129], [100, 10, 0, 40, 0], 16, 24, 8, 128, None, None),
+]
+
+
+@pytest.mark.parametrize("what,lens,starts,ps,hq,hkv,d,window,splits", CASES,
+                         ids=[c[0] for c in CASES])
+def test_tensor_core_attention_bfloat16(ops, monkeypatch, what, lens, starts, ps, hq, hkv, d,
+                                        window, splits):
+    qkv, pool, ctx, n = paged_case(lens, starts, ps, hq, hkv, d, torch.bfloat16)
+    if splits:
+        monkeypatch.setattr(ops, "plan_kv_splits", lambda *a: splits)
+    out = torch.zeros(n, hq * d, device=dev(), dtype=torch.bfloat16)
+    ops.paged_attention(qkv, pool, ctx, 0, out, hq, hkv, d, 1 / math.sqrt(d), window)
+    ref = torch.zeros(n, hq * d, device=dev())
+    twin_ops.attention_generic(qkv.float(), pool.float(), ctx.block_tables[0], ctx.tok_seq,
+                               ctx.positions, ref, hq, hkv, d, 1 / math.sqrt(d), window)
+    # the kernel rounds P to bfloat16 before P V and the result once: a few 1e-3 relative
+    assert (out.float() - ref).abs().max() < 2e-2
+
+
+def test_attention_finds_one_far_key_among_hundreds(ops):
+    """Random keys give flat softmax rows that hide a wrong page.  Here one far key (on a
+    page of its own, in the middle of the table) matches the query 30 times better than the
+    rest, so the output must be that key's value."""
+    hq, hkv, d, ps = 4, 2, 64, 16
+    for dt in (torch.float32, torch.bfloat16):
+        qkv, pool, ctx, n = paged_case([1, 70], [900, 700], ps, hq, hkv, d, dt, seed=5)
+        pool.mul_(0.05)
+        table = ctx.block_tables[0]
+        for seq, far in ((0, 437), (1, 23)):
+            page, off = int(table[seq, far // ps]), far % ps
+            toks = (ctx.tok_seq == seq).nonzero().flatten()
+            for h in range(hq):
+                kvh = h // (hq // hkv)
+                key = torch.zeros(d, device=dev())
+                key[h * 3] = 30.0
+                pool[page, 0, kvh, off, h * 3] = 30.0
+                qkv[toks, h * d:(h + 1) * d] = key.to(dt) * 1.0
+            pool[page, 1, :, off, :] = 7.0
+        out = torch.zeros(n, hq * d, device=dev(), dtype=dt)
+        ops.paged_attention(qkv, pool, ctx, 0, out, hq, hkv, d, 1 / math.sqrt(d), None)
+        assert (out.float() - 7.0).abs().max() < 0.1, f"{dt}: the far key was not found"
+
+
+def test_sampling_kernel_against_plain_sampler(ops):
+    V = 1000
+    logits = torch.randn(8, V, device=dev(), generator=gen(5)) * 3
+    logits[7, 10] = logits[7, 20] = logits[7].max() + 1            # a tie: lower index wins
+    temp = torch.tensor([0, 1.0, 0.8, 0.8, 0.8, 1.3, 2.0, 0], device=dev())
+    top_k = torch.tensor([0, 0, 50, 0, 20, 5, 1, 0], device=dev(), dtype=torch.int32)
+    top_p = torch.tensor([1.0, 1.0, 1.0, 0.9, 0.5, 0.0, 1.0, 1.0], device=dev())
+    seed = torch.arange(1, 9, device=dev(), dtype=torch.int32)
+    sid = torch.arange(9, 1, -1, device=dev(), dtype=torch.int32)
+    ctr = torch.arange(0, 8, device=dev(), dtype=torch.int32)
+    got = torch.empty(8, device=dev(), dtype=torch.int32)
+    ops.sample(logits, temp, top_k, top_p, seed, sid, ctr, got)
+    want = torch.empty(8, dtype=torch.int32)
+    twin_ops.sample(logits.cpu(), temp.cpu(), top_k.cpu(), top_p.cpu(), seed.cpu(), sid.cpu(),
+                    ctr.cpu(), want)
+    assert got.cpu().tolist() == want.tolist()
+    assert int(got[7]) == 10 and int(got[0]) == int(logits[0].argmax())
+    # a vocabulary that is no power of two and far larger than the block
+    big = torch.randn(2, 128256, device=dev(), generator=gen(6))
+    t2 = torch.tensor([0.0, 0.7], device=dev())
+    k2 = torch.tensor([0, 40], device=dev(), dtype=torch.int32)
+    p2 = torch.tensor([1.0, 0.95], device=dev())
+    z = torch.zeros(2, device=dev(), dtype=torch.int32)
+    got = torch.empty(2, device=dev(), dtype=torch.int32)
+    ops.sample(big, t2, k2, p2, z, z, z, got)
+    assert int(got[0]) == int(big[0].argmax())
+    kept = torch.isfinite(plain_llama.filter_logits(big[1].cpu(), 0.7, 40, 0.95))
+    assert bool(kept[int(got[1])])
+
+
+def test_kernels_refuse_what_they_cannot_take(ops):
+    x = torch.zeros(4, 40, device=dev())
+    with pytest.raises(ops.KernelError):
+        ops.embed_gather(torch.zeros(10, 40), torch.zeros(4, dtype=torch.int32), torch.zeros(4, 40))
+    with pytest.raises(ops.KernelError):
+        ops.linear(x, torch.zeros(8, 41, device=dev()), torch.zeros(4, 8, device=dev()))
+    with pytest.raises(ops.KernelError):
+        ops.attention_library(40)            # head sizes come in steps of 16
+    with pytest.raises(ops.KernelError):
+        ops.rmsnorm(x, torch.ones(40, device=dev()), 1e-5, torch.zeros(4, 40, device=dev()),
+                    rows=torch.zeros(4, device=dev(), dtype=torch.int64))

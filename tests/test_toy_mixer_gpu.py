@@ -1,0 +1,180 @@
+"""A mixer with state of its own, a position encoding of its own and an architecture of
+its own, all defined HERE, are registered, built, given random weights, and stepped in
+portions and mixed batches, without a change to any file of the framework.
+
+The toy mixer keeps a decaying sum per request: s <- decay * s + x_t, y_t = W s.  Its state
+is one row of fixed size per request (the cache manager's slots), so it must be carried
+across portions, zeroed when a slot is handed to a new request, and kept apart between
+requests that share a batch.
+"""
+
+from dataclasses import dataclass
+
+import pytest
+import torch
+
+from tests.conftest import random_ids
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def define_toy():
+    from simple_inference_b200 import ops
+    from simple_inference_b200.config import ModelConfig, register_architecture
+    from simple_inference_b200.models.llama import llama_layer_plan
+    from simple_inference_b200.models.plan import LayerPlan, ModelPlan
+    from simple_inference_b200.config.model_config import LlamaConfig
+    from simple_inference_b200.parts import (Mixer, PartSpec, PositionEncoding, StateSpec, TensorSpec,
+                                             register_mixer, register_position_encoding)
+
+    @register_mixer("toy_decay")
+    class DecayMixer(Mixer):
+        def __init__(self, hidden_size: int, decay: float):
+            self.hidden_size, self.decay = hidden_size, decay
+
+        def tensors(self):
+            return {"w": TensorSpec((self.hidden_size, self.hidden_size))}
+
+        def cache_spec(self):
+            return StateSpec((self.hidden_size,), "float32")
+
+        def bind(self, tensors, rt):
+            super().bind(tensors, rt)
+            self.w = tensors["w"]
+
+        def forward(self, x, ctx, cache):
+            sums = torch.empty(x.shape, dtype=torch.float32, device=x.device)
+            slots = ctx.seq_slots.tolist()
+            t = 0
+            for s, n in enumerate(ctx.q_lens):
+                state = cache.state[slots[s]]
+                for i in range(n):
+                    state.mul_(self.decay).add_(x[t + i].float())
+                    sums[t + i] = state
+                t += n
+            out = ctx.ws.get("toy.out", (x.shape[0], self.hidden_size), x.dtype)
+            return ops.linear(sums.to(x.dtype), self.w, out)
+
+    @register_position_encoding("toy_half_rotary")
+    class HalfSpeedRotary(PositionEncoding):
+        """Rotary encoding whose every frequency is one constant: another position encoding."""
+
+        def __init__(self, head_dim: int, freq: float):
+            self.head_dim, self.freq = head_dim, freq
+
+        def bind(self, tensors, rt):
+            super().bind(tensors, rt)
+            self.inv_freq = torch.full((self.head_dim // 2,), self.freq, dtype=torch.float32,
+                                       device=rt.device)
+
+        def encode_and_store(self, qkv, num_q_heads, num_kv_heads, head_dim, ctx, cache):
+            ops.rope_kv_store(qkv, ctx.positions, self.inv_freq, ctx.kv_slots[cache.group],
+                              cache.pool, num_q_heads, num_kv_heads, head_dim, cache.page_size,
+                              cache.writes)
+
+    @dataclass(kw_only=True)
+    class ToyConfig(LlamaConfig):
+        decay: float = 0.5
+        toy_freq: float = 0.25
+
+    def toy_plan(cfg: ToyConfig) -> ModelPlan:
+        layers = []
+        for i in range(cfg.num_hidden_layers):
+            lp = llama_layer_plan(cfg, i)
+            params = dict(lp.block.params)
+            if i % 2 == 1:      # odd layers: the state mixer instead of attention
+                params["mixer"] = PartSpec("toy_decay", {"hidden_size": cfg.hidden_size,
+                                                         "decay": cfg.decay})
+                names = {k: v for k, v in lp.tensor_names.items() if not k.startswith("mixer.")}
+                names["mixer.w"] = f"model.layers.{i}.toy.w"
+            else:               # even layers: attention with the toy position encoding
+                mixer = dict(params["mixer"].params)
+                mixer["position"] = PartSpec("toy_half_rotary", {"head_dim": cfg.head_dim,
+                                                                 "freq": cfg.toy_freq})
+                params["mixer"] = PartSpec("attention", mixer)
+                names = lp.tensor_names
+            layers.append(LayerPlan(PartSpec("prenorm", params), names))
+        return ModelPlan(
+            hidden_size=cfg.hidden_size, vocab_size=cfg.vocab_size, layers=layers,
+            run_order=ModelPlan.sequential(len(layers)),
+            final_norm=PartSpec("rmsnorm", {"hidden_size": cfg.hidden_size, "eps": cfg.rms_norm_eps}),
+            tie_embeddings=cfg.tie_word_embeddings, embedding_name="model.embed_tokens.weight",
+            final_norm_names={"weight": "model.norm.weight"}, head_name="lm_head.weight",
+            max_positions=cfg.max_position_embeddings)
+
+    register_architecture("ToyForCausalLM", ToyConfig, toy_plan)
+
+
+def plain_toy(cfg, w, ids):
+    """Whole-sequence plain model of the toy architecture."""
+    from tests import plain_llama as pl
+    x = w["model.embed_tokens.weight"][torch.tensor(ids)]
+    pos = list(range(len(ids)))
+    D = pl.head_dim_of(cfg)
+    freqs = torch.full((D // 2,), cfg["toy_freq"])
+    for i in range(cfg["num_hidden_layers"]):
+        p = f"model.layers.{i}."
+        h = pl.rmsnorm(x, w[p + "input_layernorm.weight"], cfg["rms_norm_eps"])
+        if i % 2 == 1:
+            s = torch.zeros(cfg["hidden_size"])
+            rows = []
+            for t in range(len(ids)):
+                s = cfg["decay"] * s + h[t]
+                rows.append(s)
+            x = x + torch.stack(rows) @ w[p + "toy.w"].T
+        else:
+            x = x + pl.attention_layer(h, w, p + "self_attn.", cfg, pos, freqs)
+        x = x + pl.mlp(pl.rmsnorm(x, w[p + "post_attention_layernorm.weight"], cfg["rms_norm_eps"]), w, p + "mlp.")
+    x = pl.rmsnorm(x, w["model.norm.weight"], cfg["rms_norm_eps"])
+    return x @ w["model.embed_tokens.weight"].T
+
+
+def test_toy_architecture_registers_builds_and_steps(tmp_path):
+    define_toy()
+    from simple_inference_b200 import load_model, write_random_model, known_architectures
+    from simple_inference_b200.cache import CacheManager
+    from simple_inference_b200.engine import ModelRunner, StepEntry
+    from simple_inference_b200.parts import PagedKVSpec, StateSpec
+    from tests import plain_llama
+    assert "ToyForCausalLM" in known_architectures()
+    config = {
+        "architectures": ["ToyForCausalLM"], "num_hidden_layers": 4, "hidden_size": 48,
+        "num_attention_heads": 3, "num_key_value_heads": 1, "head_dim": 16,
+        "intermediate_size": 72, "vocab_size": 101, "rope_theta": 10000.0, "rms_norm_eps": 1e-5,
+        "tie_word_embeddings": True, "max_position_embeddings": 128, "torch_dtype": "float32",
+        "decay": 0.75, "toy_freq": 0.125,
+    }
+    write_random_model(tmp_path, config, seed=2)
+    cfg, model = load_model(tmp_path, "float32", DEV)
+    specs = model.cache_specs()
+    assert [type(s) for s in specs] == [PagedKVSpec, StateSpec, PagedKVSpec, StateSpec]
+    cache = CacheManager(specs, 4, 30, 2, 64, torch.float32, DEV)
+    assert len(cache.groups) == 1 and sorted(cache.state) == [1, 3]
+    runner = ModelRunner(model, cache, model.rt, 64, 2, 128, max_logit_rows=64)
+    pcfg, w = plain_llama.read_folder(tmp_path)
+    seqs = [random_ids(n, 101, 20 + n) for n in (45, 30, 12)]
+    want = [plain_toy(pcfg, w, s) for s in seqs]
+    got = {i: [] for i in range(3)}
+    fed = {i: 0 for i in range(3)}
+
+    def feed(step):
+        entries = [StepEntry(i, seqs[i][fed[i]:fed[i] + n], list(range(n))) for i, n in step]
+        out = runner.step(entries).clone().cpu()
+        o = 0
+        for i, n in step:
+            got[i].append(out[o:o + n])
+            o += n
+            fed[i] += n
+
+    cache.admit(0, 45)
+    cache.admit(1, 30)
+    for step in ([(0, 20)], [(0, 1), (1, 9)], [(1, 2), (0, 5)], [(0, 19), (1, 19)]):
+        feed(step)
+    cache.release(1)                  # request 2 takes over request 1's slot and pages:
+    cache.admit(2, 12)                # its state row must start from zero
+    assert cache.slot(2) == 1
+    for step in ([(2, 3)], [(2, 1)], [(2, 8)]):
+        feed(step)
+    for i in range(3):
+        assert (torch.cat(got[i]) - want[i]).abs().max() < 2e-5, f"sequence {i}"
