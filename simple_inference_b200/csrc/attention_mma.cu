@@ -88,27 +88,37 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 __device__ __forceinline__ void load_kv_tile(bf16* sK, bf16* sV, const bf16* __restrict__ pool,
                                              const int* __restrict__ table, int key0, int k_lo,
                                              int k_hi, int kvh, int n_kv_heads, int page_size) {
-  const int tid = threadIdx.x;
-  const int row = tid >> 1, half = tid & 1;
-  const int j = key0 + row;
-  const bool valid = (j >= k_lo) && (j <= k_hi);
-  const bf16* kptr = pool;
-  const bf16* vptr = pool;
-  if (valid) {
-    const int lp = j / page_size;
-    const int page = table[lp];
-    const int off = j - lp * page_size;
-    const long long head_stride = (long long)page_size * D;
-    kptr = pool + ((long long)page * 2 * n_kv_heads + kvh) * head_stride + (long long)off * D;
-    vptr = kptr + (long long)n_kv_heads * head_stride;
-  }
-  bf16* dk = sK + row * STRIDE;
-  bf16* dv = sV + row * STRIDE;
+  // Consecutive threads copy consecutive 16-byte chunks of a row, so a warp's
+  // request covers whole rows (full sectors), not half a sector per thread.
+  const long long head_stride = (long long)page_size * D;
 #pragma unroll
-  for (int c = 0; c < CHUNKS / 2; ++c) {
-    const int chunk = half * (CHUNKS / 2) + c;
-    cp_async16(dk + chunk * 8, kptr + (valid ? chunk * 8 : 0), valid);
-    cp_async16(dv + chunk * 8, vptr + (valid ? chunk * 8 : 0), valid);
+  for (int i = 0; i < (KV_TILE * CHUNKS) / THREADS; ++i) {
+    const int idx = threadIdx.x + i * THREADS;
+    const int row = idx / CHUNKS, chunk = idx - row * CHUNKS;
+    const int j = key0 + row;
+    const bool valid = (j >= k_lo) && (j <= k_hi);
+    const bf16* kptr = pool;
+    const bf16* vptr = pool;
+    if (valid) {
+      const int lp = j / page_size;
+      const int page = table[lp];
+      const int off = j - lp * page_size;
+      kptr = pool + ((long long)page * 2 * n_kv_heads + kvh) * head_stride + (long long)off * D +
+             chunk * 8;
+      vptr = kptr + (long long)n_kv_heads * head_stride;
+    }
+    cp_async16(sK + row * STRIDE + chunk * 8, kptr, valid);
+    cp_async16(sV + row * STRIDE + chunk * 8, vptr, valid);
+  }
+}
+
+// rows [0, n_rows) of a [rows][D] tile whose row r starts at src + r * row_stride
+__device__ __forceinline__ void load_q_rows(bf16* sQ, const bf16* __restrict__ src,
+                                            long long row_stride, int n_rows, int tile_rows) {
+  for (int idx = threadIdx.x; idx < tile_rows * CHUNKS; idx += THREADS) {
+    const int row = idx / CHUNKS, chunk = idx - row * CHUNKS;
+    const bool valid = row < n_rows;
+    cp_async16(sQ + row * STRIDE + chunk * 8, src + (valid ? row * row_stride + chunk * 8 : 0), valid);
   }
 }
 
@@ -220,16 +230,8 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
   const int k_lo = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
   const int* table = block_table + (long long)seq * table_stride;
 
-  {  // Q tile; rows past n_rows are zero
-    const int row = tid >> 1, half = tid & 1;
-    const bool valid = row < n_rows;
-    const bf16* src = q + (long long)(tok0 + (valid ? row : 0)) * q_stride + (long long)h * D;
-#pragma unroll
-    for (int c = 0; c < CHUNKS / 2; ++c) {
-      const int chunk = half * (CHUNKS / 2) + c;
-      cp_async16(sQ + row * STRIDE + chunk * 8, src + chunk * 8, valid);
-    }
-  }
+  // Q tile; rows past n_rows are zero
+  load_q_rows(sQ, q + (long long)tok0 * q_stride + (long long)h * D, q_stride, n_rows, Q_TILE);
   const int tile_first = k_lo / KV_TILE, tile_last = k_hi / KV_TILE;
   load_kv_tile(sKV, sKV + KV_TILE * STRIDE, pool, table, tile_first * KV_TILE, k_lo, k_hi, kvh,
                n_kv_heads, page_size);
@@ -345,16 +347,8 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
 
   if (tile_a < tile_b) {
-    if (tid < 16 * 2) {  // Q rows: one per query head of the chunk, the rest zero
-      const int row = tid >> 1, half = tid & 1;
-      const bool valid = row < n_heads_here;
-      const bf16* src = q + (long long)tok * q_stride + (long long)(head0 + (valid ? row : 0)) * D;
-#pragma unroll
-      for (int c = 0; c < CHUNKS / 2; ++c) {
-        const int chunk = half * (CHUNKS / 2) + c;
-        cp_async16(sQ + row * STRIDE + chunk * 8, src + chunk * 8, valid);
-      }
-    }
+    // Q rows: one per query head of the chunk, the rest zero
+    load_q_rows(sQ, q + (long long)tok * q_stride + (long long)head0 * D, D, n_heads_here, 16);
     load_kv_tile(sKV, sKV + KV_TILE * STRIDE, pool, table, tile_a * KV_TILE, k_lo_all, pos, kvh,
                  n_kv_heads, page_size);
     cp_async_commit();

@@ -19,8 +19,8 @@ import torch
 
 from .build import KernelBuildError, load_library
 
-_CORE_SOURCES = ["rowwise.cu", "rope_kv.cu", "gemm_fp32.cu", "attention_generic.cu",
-                 "sampling.cu", "attention_decode.cu", "no_alloc.cu"]
+_CORE_SOURCES = ["rowwise.cu", "rope_kv.cu", "gemm_fp32.cu", "gemm_skinny.cu",
+                 "attention_generic.cu", "sampling.cu", "no_alloc.cu"]
 
 _ERRORS = {
     -1: "bad argument (null pointer, negative size or misaligned pointer)",
@@ -148,11 +148,21 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
 
 # ------------------------------------------------------------ matrix product
 
+SKINNY_MAX_ROWS = 16  # up to this many tokens the hand-written weight-streaming product runs
+
+
+def _skinny_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    return (x.is_cuda and x.dtype == torch.bfloat16 and 0 < x.shape[0] <= SKINNY_MAX_ROWS
+            and x.shape[1] % 8 == 0 and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
+            and weight.data_ptr() % 16 == 0)
+
+
 def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     """``out = x @ weight.T`` for ``weight`` in the ``[out, in]`` layout.
 
-    float32 operands: the FMA kernel (true 32-bit).  bfloat16 operands: the
-    library GEMM with float32 accumulation; ``out`` may be bfloat16 or float32.
+    float32 operands: the FMA kernel (true 32-bit).  bfloat16 operands: for up
+    to 16 rows the weight-streaming tensor-core kernel, above that the library
+    GEMM; float32 accumulation either way; ``out`` may be bfloat16 or float32.
     """
     _dev(x, weight, out)
     m, k = x.shape
@@ -165,10 +175,32 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> torch.Te
             raise KernelError("linear: float32 operands need a float32 output")
         _check(core().si_gemm_fp32_tn(_p(x), _p(weight), _p(out), m, n, k, k, k, n, _stream()),
                "gemm_fp32")
+    elif _skinny_ok(x, weight):
+        _check(core().si_gemm_skinny_bf16(_p(x), x.stride(0), _p(weight), _p(out), out.stride(0),
+                                          m, n, k, 0 if out.dtype == torch.bfloat16 else 1,
+                                          _stream()), "gemm_skinny")
     elif out.dtype == torch.bfloat16:
         torch.mm(x, weight.t(), out=out)
     else:
         torch.mm(x, weight.t(), out_dtype=torch.float32, out=out)
+    return out
+
+
+def can_fuse_swiglu(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    """Whether ``linear_swiglu`` can run for these operands (few bfloat16 rows on the GPU)."""
+    return _skinny_ok(x, weight)
+
+
+def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """``out = silu(x @ Wg.T) * (x @ Wu.T)`` with ``w_gate_up = [Wg; Wu]``, in one kernel."""
+    _dev(x, w_gate_up, out)
+    m, k = x.shape
+    inter = out.shape[1]
+    if w_gate_up.shape != (2 * inter, k) or out.shape[0] != m or out.dtype != torch.bfloat16 \
+            or not _skinny_ok(x, w_gate_up):
+        raise KernelError("linear_swiglu: operands do not fit (see can_fuse_swiglu)")
+    _check(core().si_gemm_skinny_bf16(_p(x), x.stride(0), _p(w_gate_up), _p(out), out.stride(0),
+                                      m, inter, k, 2, _stream()), "gemm_skinny_swiglu")
     return out
 
 
@@ -302,5 +334,5 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
     return out
 
 
-__all__ = ["KernelError", "KernelBuildError", "embed_gather", "rmsnorm", "swiglu", "linear",
+__all__ = ["KernelError", "KernelBuildError", "embed_gather", "rmsnorm", "swiglu", "linear", "linear_swiglu", "can_fuse_swiglu",
            "rope_kv_store", "attention_generic", "paged_attention", "plan_kv_splits", "sample", "core", "attention_library"]

@@ -38,10 +38,14 @@ class SwiGLU(FeedForward):
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         n = x.shape[0]
-        gate_up = ctx.ws.get("mlp.gate_up", (n, 2 * self.intermediate_size), x.dtype)
-        ops.linear(x, self.w_gate_up, gate_up)
         hidden = ctx.ws.get("mlp.hidden", (n, self.intermediate_size), x.dtype)
-        ops.swiglu(gate_up, hidden)
+        if ops.can_fuse_swiglu(x, self.w_gate_up):
+            # a few tokens: one weight-streaming kernel with the gate fused in
+            ops.linear_swiglu(x, self.w_gate_up, hidden)
+        else:
+            gate_up = ctx.ws.get("mlp.gate_up", (n, 2 * self.intermediate_size), x.dtype)
+            ops.linear(x, self.w_gate_up, gate_up)
+            ops.swiglu(gate_up, hidden)
         out = ctx.ws.get("mlp.down", (n, self.hidden_size), x.dtype)
         ops.linear(hidden, self.w_down, out)
         return out

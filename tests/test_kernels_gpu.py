@@ -259,3 +259,30 @@ def test_kernels_refuse_what_they_cannot_take(ops):
     with pytest.raises(ops.KernelError):
         ops.rmsnorm(x, torch.ones(40, device=dev()), 1e-5, torch.zeros(4, 40, device=dev()),
                     rows=torch.zeros(4, device=dev(), dtype=torch.int64))
+
+
+@pytest.mark.parametrize("m", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("n,k", [(50, 64), (331, 120), (5120, 3072), (16, 8), (3072, 8192)])
+def test_weight_streaming_product_for_few_rows(ops, m, n, k):
+    """The hand-written product that decode steps use (M <= 16), all three epilogues."""
+    g = gen(7)
+    x = (torch.randn(m, k, device=dev(), generator=g) * 0.5).bfloat16()
+    w = (torch.randn(2 * n, k, device=dev(), generator=g) * 0.1).bfloat16()
+    ref = x.float() @ w.float().T                       # [m, 2n]
+    scale = max(1.0, float(ref.abs().max()))
+    assert ops.can_fuse_swiglu(x, w)
+    out = torch.empty(m, 2 * n, device=dev(), dtype=torch.bfloat16)
+    ops.linear(x, w, out)
+    assert (out.float() - ref).abs().max() < 8e-3 * scale      # one bfloat16 rounding of the result
+    out32 = torch.empty(m, 2 * n, device=dev())
+    ops.linear(x, w, out32)
+    assert (out32 - ref).abs().max() < 1e-4 * scale            # float32 accumulation, no rounding
+    fused = torch.empty(m, n, device=dev(), dtype=torch.bfloat16)
+    ops.linear_swiglu(x, w, fused)
+    gate, up = ref[:, :n], ref[:, n:]
+    want = gate * torch.sigmoid(gate) * up
+    assert (fused.float() - want).abs().max() < 8e-3 * max(1.0, float(want.abs().max()))
+    # a row's result does not depend on how many rows ride along
+    one = torch.empty(1, 2 * n, device=dev())
+    ops.linear(x[m - 1:m], w, one)
+    assert torch.equal(one[0], out32[m - 1])
