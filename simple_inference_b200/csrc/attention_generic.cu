@@ -158,17 +158,16 @@ SI_API int si_attention_generic(const void* q, int q_stride, const void* pool,
   const size_t smem = (size_t)head_dim * sizeof(float) + si::ATT_THREADS * sizeof(float) +
                       si::ATT_THREADS * sizeof(long long);
   if (dtype == SI_F32)
-    si::attn_generic_kernel<float><<<grid, si::ATT_THREADS, smem, stream>>>(
+    SI_LAUNCH(si::attn_generic_kernel<float>, grid, si::ATT_THREADS, smem, stream,
         (const float*)q, q_stride, (const float*)pool, block_table, table_stride, tok_seq,
         positions, (float*)out, out_stride, n_q_heads, n_kv_heads, head_dim, page_size, scale,
         window);
   else if (dtype == SI_BF16)
-    si::attn_generic_kernel<__nv_bfloat16><<<grid, si::ATT_THREADS, smem, stream>>>(
+    SI_LAUNCH(si::attn_generic_kernel<__nv_bfloat16>, grid, si::ATT_THREADS, smem, stream,
         (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)pool, block_table, table_stride,
         tok_seq, positions, (__nv_bfloat16*)out, out_stride, n_q_heads, n_kv_heads, head_dim,
         page_size, scale, window);
   else
     return SI_ERR_DTYPE;
-  SI_LAUNCH_CHECK();
   return SI_OK;
 }

@@ -493,11 +493,10 @@ SI_API int si_attn_prefill(const void* q, int q_stride, const void* pool, const 
     configured = true;
   }
   dim3 grid(n_tiles, n_q_heads);
-  si::attn_prefill_kernel<<<grid, si::THREADS, si::PREFILL_SMEM, stream>>>(
+  SI_LAUNCH(si::attn_prefill_kernel, grid, si::THREADS, si::PREFILL_SMEM, stream,
       (const si::bf16*)q, q_stride, (const si::bf16*)pool, block_table, table_stride, cu_q,
       positions, tile_seq, tile_start, (si::bf16*)out, out_stride, n_q_heads, n_kv_heads,
       page_size, scale * si::LOG2E, window);
-  SI_LAUNCH_CHECK();
   return SI_OK;
 }
 
@@ -535,16 +534,14 @@ SI_API int si_attn_decode(const void* q, int q_stride, const void* pool, const i
   float* part_acc = scratch;
   float* part_ml = scratch ? scratch + (long long)n_single * n_q_heads * n_splits * si::D : nullptr;
   dim3 grid(n_single, grid_y, n_splits);
-  si::attn_decode_kernel<<<grid, si::THREADS, si::DECODE_SMEM, stream>>>(
+  SI_LAUNCH(si::attn_decode_kernel, grid, si::THREADS, si::DECODE_SMEM, stream,
       (const si::bf16*)q, q_stride, (const si::bf16*)pool, block_table, table_stride, cu_q,
       positions, single_seqs, (si::bf16*)out, out_stride, part_acc, part_ml, n_q_heads, n_kv_heads,
       page_size, scale * si::LOG2E, window, n_splits);
-  SI_LAUNCH_CHECK();
   if (n_splits > 1) {
     dim3 mgrid(n_single, n_q_heads);
-    si::attn_merge_kernel<<<mgrid, si::D >= 128 ? 128 : 64, 0, stream>>>(
+    SI_LAUNCH(si::attn_merge_kernel, mgrid, si::D >= 128 ? 128 : 64, 0, stream,
         part_acc, part_ml, cu_q, single_seqs, (si::bf16*)out, out_stride, n_q_heads, n_splits);
-    SI_LAUNCH_CHECK();
-  }
+    }
   return SI_OK;
 }

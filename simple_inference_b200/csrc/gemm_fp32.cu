@@ -79,7 +79,6 @@ SI_API int si_gemm_fp32_tn(const float* A, const float* W, float* C, int M, int 
   if (M == 0) return SI_OK;
   dim3 grid((N + si::BN - 1) / si::BN, (M + si::BM - 1) / si::BM);
   if (grid.y > 65535) return SI_ERR_TOO_LARGE;
-  si::gemm_fp32_tn_kernel<<<grid, 256, 0, stream>>>(A, W, C, M, N, K, lda, ldw, ldc);
-  SI_LAUNCH_CHECK();
+  SI_LAUNCH(si::gemm_fp32_tn_kernel, grid, 256, 0, stream, A, W, C, M, N, K, lda, ldw, ldc);
   return SI_OK;
 }

@@ -28,7 +28,10 @@ namespace si {
 typedef __nv_bfloat16 bf16;
 constexpr int SK_THREADS = 256;
 constexpr int SK_WARPS = 8;
-constexpr int SK_UNROLL = 4;
+#ifndef SI_SK_UNROLL
+#define SI_SK_UNROLL 4
+#endif
+constexpr int SK_UNROLL = SI_SK_UNROLL;
 
 enum SkinnyEpilogue { SK_BF16 = 0, SK_F32 = 1, SK_SWIGLU = 2 };
 
@@ -90,24 +93,34 @@ skinny_gemm_kernel(const bf16* __restrict__ X, int ldx, const bf16* __restrict__
 #pragma unroll
       for (int e = 0; e < 4; ++e) acc[mt][nt][e] = 0.0f;
 
+  // Software pipeline over batches of SK_UNROLL steps: the weights of batch i+1
+  // are requested before batch i is multiplied, so a warp keeps two batches
+  // (8 steps, 8 KB) in flight.  Step s of this warp is global step kw + s*warps_k.
   const int n_steps = (K + 31) / 32;
-  for (int c0 = kw; c0 < n_steps; c0 += warps_k * SK_UNROLL) {
-    uint4 a[SK_UNROLL][MT][2];
+  const int my_steps = (n_steps - kw + warps_k - 1) / warps_k;
+  const int n_batches = (my_steps + SK_UNROLL - 1) / SK_UNROLL;
+
+  uint4 a0[SK_UNROLL][MT][2], a1[SK_UNROLL][MT][2];
+  auto load_a = [&](uint4 (&a)[SK_UNROLL][MT][2], int batch) {
+#pragma unroll
+    for (int u = 0; u < SK_UNROLL; ++u) {
+      const int k = (kw + (batch * SK_UNROLL + u) * warps_k) * 32 + t * 8;
+      const bool ok = k < K;  // K is a multiple of 8: a lane's 8 values are all in or all out
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        a[u][mt][0] = ok ? ldg_stream(wrow[mt][0] + k) : make_uint4(0, 0, 0, 0);
+        a[u][mt][1] = ok ? ldg_stream(wrow[mt][1] + k) : make_uint4(0, 0, 0, 0);
+      }
+    }
+  };
+  auto multiply = [&](const uint4 (&a)[SK_UNROLL][MT][2], int batch) {
     uint4 b[SK_UNROLL][NT];
 #pragma unroll
     for (int u = 0; u < SK_UNROLL; ++u) {
-      const int k = (c0 + u * warps_k) * 32 + t * 8;
-      const bool ok = k < K;  // K is a multiple of 8: a lane's 8 values are all in or all out
-      const int ks = ok ? k : 0;
+      const int k = (kw + (batch * SK_UNROLL + u) * warps_k) * 32 + t * 8;
 #pragma unroll
-      for (int mt = 0; mt < MT; ++mt) {
-        a[u][mt][0] = ldg_stream(wrow[mt][0] + ks);
-        a[u][mt][1] = ldg_stream(wrow[mt][1] + ks);
-      }
-#pragma unroll
-      for (int nt = 0; nt < NT; ++nt) {
-        b[u][nt] = ok ? *reinterpret_cast<const uint4*>(xrow[nt] + ks) : make_uint4(0, 0, 0, 0);
-      }
+      for (int nt = 0; nt < NT; ++nt)
+        b[u][nt] = (k < K) ? *reinterpret_cast<const uint4*>(xrow[nt] + k) : make_uint4(0, 0, 0, 0);
     }
 #pragma unroll
     for (int u = 0; u < SK_UNROLL; ++u)
@@ -120,6 +133,23 @@ skinny_gemm_kernel(const bf16* __restrict__ X, int ldx, const bf16* __restrict__
           mma16816(acc[mt][nt], a[u][mt][0].z, a[u][mt][1].z, a[u][mt][0].w, a[u][mt][1].w,
                    b[u][nt].z, b[u][nt].w);
         }
+  };
+
+  if (MT == 2) {
+    // two weight tiles per warp: the second buffer would cost a resident block per SM,
+    // which measures slower than the latency it hides
+    for (int batch = 0; batch < n_batches; ++batch) {
+      load_a(a0, batch);
+      multiply(a0, batch);
+    }
+  } else {
+    load_a(a0, 0);
+    for (int batch = 0; batch < n_batches; batch += 2) {
+      load_a(a1, batch + 1);   // steps past the end load nothing
+      multiply(a0, batch);
+      load_a(a0, batch + 2);
+      multiply(a1, batch + 1);
+    }
   }
 
   // partial sums of this warp: rows g, g+8 of each tile, tokens 2t, 2t+1 of each n-tile
@@ -165,9 +195,8 @@ static int launch_skinny(const void* X, int ldx, const void* W, void* out, int l
   while (warps_n > 1 && (N + warps_n * 16 - 1) / (warps_n * 16) < 2 * 148) warps_n >>= 1;
   const int warps_k = SK_WARPS / warps_n;
   const int blocks = (N + warps_n * 16 - 1) / (warps_n * 16);
-  skinny_gemm_kernel<NT, EPI><<<blocks, SK_THREADS, 0, stream>>>(
-      (const bf16*)X, ldx, (const bf16*)W, out, ldo, M, N, K, warps_k);
-  SI_LAUNCH_CHECK();
+  SI_LAUNCH((skinny_gemm_kernel<NT, EPI>), blocks, SK_THREADS, 0, stream, (const bf16*)X, ldx,
+            (const bf16*)W, out, ldo, M, N, K, warps_k);
   return SI_OK;
 }
 

@@ -42,16 +42,24 @@ __global__ void rope_kv_store_kernel(T* __restrict__ qkv, const int* __restrict_
 
   const int row_width = (n_q_heads + 2 * n_kv_heads) * head_dim;
   T* row = qkv + (size_t)t * row_width;
+  // head_dim is a multiple of 16, so a half is a multiple of 8: a thread rotates 8 pairs
+  const int groups = half / 8;
 
   // queries: rotate in place
-  const int q_pairs = n_q_heads * half;
-  for (int w = threadIdx.x; w < q_pairs; w += blockDim.x) {
-    const int h = w / half, i = w - h * half;
-    T* p = row + h * head_dim;
-    const float a = to_f32<T>(p[i]), b = to_f32<T>(p[i + half]);
-    const float c = s_cos[i], s = s_sin[i];
-    p[i] = from_f32<T>(a * c - b * s);
-    p[i + half] = from_f32<T>(b * c + a * s);
+  for (int w = threadIdx.x; w < n_q_heads * groups; w += blockDim.x) {
+    const int h = w / groups, i = (w - h * groups) * 8;
+    T* p = row + h * head_dim + i;
+    float a[8], b[8], ra[8], rb[8];
+    load8<T>(p, a);
+    load8<T>(p + half, b);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float c = s_cos[i + j], s = s_sin[i + j];
+      ra[j] = a[j] * c - b[j] * s;
+      rb[j] = b[j] * c + a[j] * s;
+    }
+    store8<T>(p, ra);
+    store8<T>(p + half, rb);
   }
   if (!write_kv) return;
 
@@ -63,20 +71,28 @@ __global__ void rope_kv_store_kernel(T* __restrict__ qkv, const int* __restrict_
   const T* krow = row + n_q_heads * head_dim;
   const T* vrow = krow + n_kv_heads * head_dim;
 
-  const int k_pairs = n_kv_heads * half;
-  for (int w = threadIdx.x; w < k_pairs; w += blockDim.x) {
-    const int h = w / half, i = w - h * half;
-    const T* p = krow + h * head_dim;
-    const float a = to_f32<T>(p[i]), b = to_f32<T>(p[i + half]);
-    const float c = s_cos[i], s = s_sin[i];
-    T* dst = kpage + h * head_stride;
-    dst[i] = from_f32<T>(a * c - b * s);
-    dst[i + half] = from_f32<T>(b * c + a * s);
+  for (int w = threadIdx.x; w < n_kv_heads * groups; w += blockDim.x) {
+    const int h = w / groups, i = (w - h * groups) * 8;
+    const T* p = krow + h * head_dim + i;
+    float a[8], b[8], ra[8], rb[8];
+    load8<T>(p, a);
+    load8<T>(p + half, b);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float c = s_cos[i + j], s = s_sin[i + j];
+      ra[j] = a[j] * c - b[j] * s;
+      rb[j] = b[j] * c + a[j] * s;
+    }
+    T* dst = kpage + h * head_stride + i;
+    store8<T>(dst, ra);
+    store8<T>(dst + half, rb);
   }
-  const int v_elems = n_kv_heads * head_dim;
-  for (int w = threadIdx.x; w < v_elems; w += blockDim.x) {
-    const int h = w / head_dim, d = w - h * head_dim;
-    vpage[h * head_stride + d] = vrow[w];
+  const int v_groups = head_dim / 8;
+  for (int w = threadIdx.x; w < n_kv_heads * v_groups; w += blockDim.x) {
+    const int h = w / v_groups, d = (w - h * v_groups) * 8;
+    float v[8];
+    load8<T>(vrow + h * head_dim + d, v);
+    store8<T>(vpage + h * head_stride + d, v);
   }
 }
 
@@ -87,24 +103,27 @@ SI_API int si_rope_kv_store(void* qkv, const int* positions, const float* inv_fr
                             int n_kv_heads, int head_dim, int page_size, int write_kv, int dtype,
                             cudaStream_t stream) {
   if (!qkv || !positions || !inv_freq || n_tokens < 0 || n_q_heads <= 0 || n_kv_heads <= 0 ||
-      head_dim <= 0 || (head_dim & 1))
+      head_dim <= 0)
     return SI_ERR_ARG;
+  if (head_dim % 16 != 0) return SI_ERR_UNSUPPORTED;
+  if ((((uintptr_t)qkv | (uintptr_t)pool) & 31) != 0) return SI_ERR_ARG;
   if (write_kv && (!kv_slots || !pool || page_size <= 0)) return SI_ERR_ARG;
   if (n_tokens == 0) return SI_OK;
   const size_t smem = (size_t)head_dim * sizeof(float);
   if (smem > 48 * 1024) return SI_ERR_TOO_LARGE;
-  const int work = n_q_heads * (head_dim / 2);
-  const int threads = work >= 1024 ? 256 : 128;
+  const int work = n_q_heads * (head_dim / 16);
+  int threads = (work + 31) / 32 * 32;
+  if (threads > 256) threads = 256;
+  if (threads < 64) threads = 64;
   if (dtype == SI_F32)
-    si::rope_kv_store_kernel<float><<<n_tokens, threads, smem, stream>>>(
-        (float*)qkv, positions, inv_freq, kv_slots, (float*)pool, n_q_heads, n_kv_heads, head_dim,
-        page_size, write_kv);
+    SI_LAUNCH(si::rope_kv_store_kernel<float>, n_tokens, threads, smem, stream, (float*)qkv,
+              positions, inv_freq, kv_slots, (float*)pool, n_q_heads, n_kv_heads, head_dim,
+              page_size, write_kv);
   else if (dtype == SI_BF16)
-    si::rope_kv_store_kernel<__nv_bfloat16><<<n_tokens, threads, smem, stream>>>(
-        (__nv_bfloat16*)qkv, positions, inv_freq, kv_slots, (__nv_bfloat16*)pool, n_q_heads,
-        n_kv_heads, head_dim, page_size, write_kv);
+    SI_LAUNCH(si::rope_kv_store_kernel<__nv_bfloat16>, n_tokens, threads, smem, stream,
+              (__nv_bfloat16*)qkv, positions, inv_freq, kv_slots, (__nv_bfloat16*)pool, n_q_heads,
+              n_kv_heads, head_dim, page_size, write_kv);
   else
     return SI_ERR_DTYPE;
-  SI_LAUNCH_CHECK();
   return SI_OK;
 }

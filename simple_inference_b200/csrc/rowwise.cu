@@ -33,7 +33,7 @@ __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __re
 //   x = residual[src] (+ delta[src]);  if (!rows && delta) residual[src] = x;
 //   out[r] = x * rsqrt(sum(x^2)/H + eps) * w
 // The row is kept in shared memory between the two passes.
-template <typename TA, typename TW>
+template <typename TA, typename TW, bool VEC>
 __global__ void rmsnorm_kernel(float* __restrict__ residual, const TA* __restrict__ delta,
                                const TW* __restrict__ weight, const int* __restrict__ rows,
                                TA* __restrict__ out, int hidden, float eps) {
@@ -44,37 +44,74 @@ __global__ void rmsnorm_kernel(float* __restrict__ residual, const TA* __restric
   float* res = residual + (size_t)src * hidden;
   const TA* del = delta ? delta + (size_t)src * hidden : nullptr;
   const bool write_back = (rows == nullptr) && (delta != nullptr);
+  TA* dst = out + (size_t)r * hidden;
   float ss = 0.0f;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-    float x = res[i];
-    if (del) {
-      x += to_f32<TA>(del[i]);
-      if (write_back) res[i] = x;
+  if (VEC) {  // hidden is a multiple of 8: 8 elements per thread and step
+    for (int i = threadIdx.x * 8; i < hidden; i += blockDim.x * 8) {
+      float x[8];
+      load8<float>(res + i, x);
+      if (del) {
+        float d[8];
+        load8<TA>(del + i, d);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) x[j] += d[j];
+        if (write_back) store8<float>(res + i, x);
+      }
+      store8<float>(srow + i, x);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) ss += x[j] * x[j];
     }
-    srow[i] = x;
-    ss += x * x;
+  } else {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+      float x = res[i];
+      if (del) {
+        x += to_f32<TA>(del[i]);
+        if (write_back) res[i] = x;
+      }
+      srow[i] = x;
+      ss += x * x;
+    }
   }
   const float total = block_sum(ss, red);
   const float rstd = rsqrtf(total / (float)hidden + eps);
-  TA* dst = out + (size_t)r * hidden;
-  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-    dst[i] = from_f32<TA>((srow[i] * rstd) * to_f32<TW>(weight[i]));
+  if (VEC) {
+    for (int i = threadIdx.x * 8; i < hidden; i += blockDim.x * 8) {
+      float x[8], w[8];
+      load8<float>(srow + i, x);
+      load8<TW>(weight + i, w);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[j] = (x[j] * rstd) * w[j];
+      store8<TA>(dst + i, x);
+    }
+  } else {
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+      dst[i] = from_f32<TA>((srow[i] * rstd) * to_f32<TW>(weight[i]));
   }
 }
 
 // ------------------------------------------------------------------- SwiGLU
 // gu is [rows, 2*inter]: gate in columns [0, inter), up in [inter, 2*inter).
-template <typename T>
+template <typename T, bool VEC>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, long long total,
                               int inter) {
-  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
-       idx += (long long)gridDim.x * blockDim.x) {
+  constexpr int W = VEC ? 8 : 1;  // inter is a multiple of 8 when VEC
+  for (long long idx = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * W; idx < total;
+       idx += (long long)gridDim.x * blockDim.x * W) {
     const long long row = idx / inter;
     const int col = (int)(idx - row * inter);
-    const float g = to_f32<T>(gu[row * 2 * inter + col]);
-    const float u = to_f32<T>(gu[row * 2 * inter + inter + col]);
-    const float s = g / (1.0f + expf(-g));
-    out[idx] = from_f32<T>(s * u);
+    const T* gp = gu + row * 2 * inter + col;
+    if (VEC) {
+      float g[8], u[8];
+      load8<T>(gp, g);
+      load8<T>(gp + inter, u);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) g[j] = (g[j] / (1.0f + expf(-g[j]))) * u[j];
+      store8<T>(out + idx, g);
+    } else {
+      const float g = to_f32<T>(gp[0]);
+      const float u = to_f32<T>(gp[inter]);
+      out[idx] = from_f32<T>((g / (1.0f + expf(-g))) * u);
+    }
   }
 }
 
@@ -86,14 +123,13 @@ SI_API int si_embed_gather(const void* table, int table_dtype, const int* ids, f
   if (n_tokens == 0) return SI_OK;
   const int threads = hidden >= 1024 ? 256 : 128;
   if (table_dtype == SI_F32)
-    si::embed_gather_kernel<float><<<n_tokens, threads, 0, stream>>>(
-        (const float*)table, ids, out, hidden, vocab);
+    SI_LAUNCH(si::embed_gather_kernel<float>, n_tokens, threads, 0, stream, (const float*)table,
+              ids, out, hidden, vocab);
   else if (table_dtype == SI_BF16)
-    si::embed_gather_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(
-        (const __nv_bfloat16*)table, ids, out, hidden, vocab);
+    SI_LAUNCH(si::embed_gather_kernel<__nv_bfloat16>, n_tokens, threads, 0, stream,
+              (const __nv_bfloat16*)table, ids, out, hidden, vocab);
   else
     return SI_ERR_DTYPE;
-  SI_LAUNCH_CHECK();
   return SI_OK;
 }
 
@@ -102,15 +138,19 @@ static int launch_rmsnorm(float* residual, const void* delta, const void* weight
                           void* out, int n_rows, int hidden, float eps, cudaStream_t stream) {
   const size_t smem = (size_t)hidden * sizeof(float);
   if (smem > 200 * 1024) return SI_ERR_TOO_LARGE;
-  auto kern = si::rmsnorm_kernel<TA, TW>;
+  const bool vec = hidden % 8 == 0 &&
+                   ((((uintptr_t)residual | (uintptr_t)delta | (uintptr_t)weight | (uintptr_t)out) & 15) == 0);
+  auto kern = vec ? si::rmsnorm_kernel<TA, TW, true> : si::rmsnorm_kernel<TA, TW, false>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return (int)e;
   }
-  const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
-  kern<<<n_rows, threads, smem, stream>>>(residual, (const TA*)delta, (const TW*)weight, rows,
-                                          (TA*)out, hidden, eps);
-  SI_LAUNCH_CHECK();
+  const int per_thread = vec ? 8 : 1;
+  int threads = (hidden / per_thread + 31) / 32 * 32;
+  if (threads > 512) threads = 512;
+  if (threads < 64) threads = 64;
+  SI_LAUNCH(kern, n_rows, threads, smem, stream, residual, (const TA*)delta, (const TW*)weight,
+            rows, (TA*)out, hidden, eps);
   return SI_OK;
 }
 
@@ -136,16 +176,25 @@ SI_API int si_swiglu(const void* gu, void* out, int n_rows, int inter, int dtype
   if (!gu || !out || n_rows < 0 || inter <= 0) return SI_ERR_ARG;
   if (n_rows == 0) return SI_OK;
   const long long total = (long long)n_rows * inter;
+  const bool vec = inter % 8 == 0 && ((((uintptr_t)gu | (uintptr_t)out) & 31) == 0);
   const int threads = 256;
-  long long blocks = (total + threads - 1) / threads;
-  if (blocks > 148LL * 32) blocks = 148LL * 32;
-  if (dtype == SI_F32)
-    si::swiglu_kernel<float><<<(int)blocks, threads, 0, stream>>>((const float*)gu, (float*)out, total, inter);
-  else if (dtype == SI_BF16)
-    si::swiglu_kernel<__nv_bfloat16><<<(int)blocks, threads, 0, stream>>>(
-        (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, total, inter);
-  else
+  long long blocks = (total / (vec ? 8 : 1) + threads - 1) / threads;
+  if (blocks > 148LL * 16) blocks = 148LL * 16;
+  if (blocks < 1) blocks = 1;
+  if (dtype == SI_F32) {
+    if (vec)
+      SI_LAUNCH((si::swiglu_kernel<float, true>), (int)blocks, threads, 0, stream, (const float*)gu, (float*)out, total, inter);
+    else
+      SI_LAUNCH((si::swiglu_kernel<float, false>), (int)blocks, threads, 0, stream, (const float*)gu, (float*)out, total, inter);
+  } else if (dtype == SI_BF16) {
+    if (vec)
+      SI_LAUNCH((si::swiglu_kernel<__nv_bfloat16, true>), (int)blocks, threads, 0, stream,
+                (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, total, inter);
+    else
+      SI_LAUNCH((si::swiglu_kernel<__nv_bfloat16, false>), (int)blocks, threads, 0, stream,
+                (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, total, inter);
+  } else {
     return SI_ERR_DTYPE;
-  SI_LAUNCH_CHECK();
+  }
   return SI_OK;
 }

@@ -182,8 +182,7 @@ SI_API int si_sample(const float* logits, int n_rows, int vocab, int ld, const f
   if (n_rows < 0 || vocab <= 0 || ld < vocab) return SI_ERR_ARG;
   if (vocab > (1 << 24)) return SI_ERR_TOO_LARGE;
   if (n_rows == 0) return SI_OK;
-  si::sample_kernel<<<n_rows, si::SAMPLE_THREADS, 0, stream>>>(
-      logits, vocab, ld, temperature, top_k, top_p, seed, stream_id, counter, out);
-  SI_LAUNCH_CHECK();
+  SI_LAUNCH(si::sample_kernel, n_rows, si::SAMPLE_THREADS, 0, stream, logits, vocab, ld,
+            temperature, top_k, top_p, seed, stream_id, counter, out);
   return SI_OK;
 }

@@ -256,16 +256,25 @@ def attention_generic(q: torch.Tensor, pool: torch.Tensor, block_table: torch.Te
 
 
 MAX_KV_SPLITS = 32
-_TARGET_BLOCKS = 2 * 148  # two resident blocks on each of the 148 SMs
+_RESIDENT_BLOCKS = 3 * 148  # decode-attention blocks that fit on the GPU at once (3 per SM)
 
 
 def plan_kv_splits(n_single: int, num_q_heads: int, num_kv_heads: int, max_kv_len: int) -> int:
-    """How many blocks share the keys of one (sequence, kv head) in the decode kernel."""
+    """How many blocks share the keys of one (sequence, kv head) in the decode kernel.
+
+    A block should see about two 64-key tiles: short blocks keep many loads in
+    flight and many waves hide the last, partly filled one.  When even that
+    leaves SMs idle, one tile per block; when there are waves enough already,
+    fewer and longer blocks.
+    """
     group = num_q_heads // num_kv_heads
     base = max(1, n_single * num_kv_heads * ((group + 15) // 16))
     tiles = max(1, (max_kv_len + 63) // 64)
-    want = (_TARGET_BLOCKS + base - 1) // base
-    return max(1, min(MAX_KV_SPLITS, tiles, want))
+    splits = max(1, tiles // 2)
+    if base * splits < _RESIDENT_BLOCKS:
+        splits = tiles
+    enough = (8 * _RESIDENT_BLOCKS + base - 1) // base
+    return max(1, min(MAX_KV_SPLITS, splits, max(enough, 1)))
 
 
 def paged_attention(q: torch.Tensor, pool: torch.Tensor, ctx, group: int, out: torch.Tensor,
