@@ -545,3 +545,42 @@ SI_API int si_attn_decode(const void* q, int q_stride, const void* pool, const i
     }
   return SI_OK;
 }
+
+// ---------------------------------------------------------------------------
+// The variant that allocates nothing (declared and explained in no_alloc.h).
+// ---------------------------------------------------------------------------
+#include "no_alloc.h"
+
+// In host code this name is only a handle for cudaGetSymbolAddress, never an address
+// to hand to a kernel.
+static __device__ __align__(256) float si_static_scratch[SI_ATTN_STATIC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_static_scratch[kMaxDevices];  // device address of si_static_scratch, per device
+}  // namespace
+
+SI_API int si_attn_decode_static(const void* q, int q_stride, const void* pool,
+                                 const int* block_table, int table_stride, const int* cu_q,
+                                 const int* positions, const int* single_seqs, int n_single,
+                                 void* out, int out_stride, int n_q_heads, int n_kv_heads,
+                                 int page_size, float scale, int window, int n_splits,
+                                 cudaStream_t stream) {
+  if (n_single < 0 || n_q_heads <= 0 || n_splits < 1) return SI_ERR_ARG;
+  if (si_attn_decode_scratch_floats(n_single, n_q_heads, n_splits) > SI_ATTN_STATIC_SCRATCH_FLOATS)
+    return SI_ERR_TOO_LARGE;
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kMaxDevices) return SI_ERR_TOO_LARGE;
+  if (g_static_scratch[dev] == nullptr) {  // set-up, once per device, with that device current
+    float* ptr = nullptr;
+    e = cudaGetSymbolAddress((void**)&ptr, si_static_scratch);
+    if (e != cudaSuccess) return (int)e;
+    if (ptr == nullptr) return SI_ERR_ARG;
+    g_static_scratch[dev] = ptr;
+  }
+  return si_attn_decode(q, q_stride, pool, block_table, table_stride, cu_q, positions, single_seqs,
+                        n_single, out, out_stride, g_static_scratch[dev], n_q_heads, n_kv_heads,
+                        page_size, scale, window, n_splits, stream);
+}

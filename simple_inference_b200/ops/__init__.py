@@ -20,7 +20,7 @@ import torch
 from .build import KernelBuildError, load_library
 
 _CORE_SOURCES = ["rowwise.cu", "rope_kv.cu", "gemm_fp32.cu", "gemm_skinny.cu",
-                 "attention_generic.cu", "sampling.cu", "no_alloc.cu"]
+                 "attention_generic.cu", "sampling.cu"]
 
 _ERRORS = {
     -1: "bad argument (null pointer, negative size or misaligned pointer)",
