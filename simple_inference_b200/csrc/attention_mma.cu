@@ -40,7 +40,9 @@ namespace si {
 constexpr int D = SI_HEAD_DIM;
 static_assert(D % 16 == 0 && D >= 16 && D <= 256, "head size must be a multiple of 16 in [16, 256]");
 constexpr int STRIDE = D + 8;        // elements per shared-memory row
-constexpr int KV_TILE = 64;          // keys per tile
+constexpr int KV_TILE = 64;          // keys per tile of the decode kernel
+constexpr int PF_TILE = 32;          // keys per tile of the prefill kernel
+constexpr int PF_STAGES = 3;         // tiles in flight in the prefill kernel
 constexpr int Q_TILE = 64;           // query rows per prefill block
 constexpr int THREADS = 128;
 constexpr int CHUNKS = D / 8;        // 16-byte chunks per row
@@ -85,6 +87,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // Keys [key0, key0+64) of one sequence and one kv head into sK, sV.  Keys
 // outside [k_lo, k_hi] are zero-filled and their pages are not touched (a page
 // before the window may already belong to someone else).
+template <int ROWS>
 __device__ __forceinline__ void load_kv_tile(bf16* sK, bf16* sV, const bf16* __restrict__ pool,
                                              const int* __restrict__ table, int key0, int k_lo,
                                              int k_hi, int kvh, int n_kv_heads, int page_size) {
@@ -92,8 +95,9 @@ __device__ __forceinline__ void load_kv_tile(bf16* sK, bf16* sV, const bf16* __r
   // request covers whole rows (full sectors), not half a sector per thread.
   const long long head_stride = (long long)page_size * D;
 #pragma unroll
-  for (int i = 0; i < (KV_TILE * CHUNKS) / THREADS; ++i) {
+  for (int i = 0; i < (ROWS * CHUNKS + THREADS - 1) / THREADS; ++i) {
     const int idx = threadIdx.x + i * THREADS;
+    if ((ROWS * CHUNKS) % THREADS != 0 && idx >= ROWS * CHUNKS) break;
     const int row = idx / CHUNKS, chunk = idx - row * CHUNKS;
     const int j = key0 + row;
     const bool valid = (j >= k_lo) && (j <= k_hi);
@@ -207,20 +211,32 @@ __device__ __forceinline__ void softmax_update(float (&s)[NT][4], float (&m)[2],
 }
 
 // ------------------------------------------------------------------- prefill
+// grid (pairs of 64-query tiles, query heads).  With a causal mask the later tiles
+// of a prompt see the most keys; the host pairs the longest tile with the
+// shortest, the second longest with the second shortest and so on (tile_pairs),
+// and a block runs its two tiles one after the other, so that all blocks take
+// about the same time and none is left running alone at the end.  Keys come in
+// tiles of 32 through a three-stage cp.async ring (one barrier per tile): small
+// tiles keep the score registers few, so three blocks fit on an SM.
 __global__ void __launch_bounds__(THREADS)
 attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restrict__ pool,
                     const int* __restrict__ block_table, int table_stride,
                     const int* __restrict__ cu_q, const int* __restrict__ positions,
                     const int* __restrict__ tile_seq, const int* __restrict__ tile_start,
-                    bf16* __restrict__ out, int out_stride, int n_q_heads, int n_kv_heads,
-                    int page_size, float scale_log2, int window) {
+                    const int* __restrict__ tile_pairs, bf16* __restrict__ out, int out_stride,
+                    int n_q_heads, int n_kv_heads, int page_size, float scale_log2, int window) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   bf16* sQ = reinterpret_cast<bf16*>(smem_raw);          // [Q_TILE][STRIDE]
-  bf16* sKV = sQ + Q_TILE * STRIDE;                      // 2 stages x (K, V) x [KV_TILE][STRIDE]
+  bf16* sKV = sQ + Q_TILE * STRIDE;                      // PF_STAGES x (K, V) x [PF_TILE][STRIDE]
+  constexpr int STAGE_ELEMS = 2 * PF_TILE * STRIDE;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int seq = tile_seq[blockIdx.x];
-  const int tok0 = cu_q[seq] + tile_start[blockIdx.x];
+  for (int which = 0; which < 2; ++which) {
+  const int tile_id = tile_pairs[2 * blockIdx.x + which];
+  if (tile_id < 0) break;
+  if (which) __syncthreads();  // the first tile's shared memory is free to reuse
+  const int seq = tile_seq[tile_id];
+  const int tok0 = cu_q[seq] + tile_start[tile_id];
   int n_rows = cu_q[seq + 1] - tok0;
   if (n_rows > Q_TILE) n_rows = Q_TILE;
   const int h = blockIdx.y;
@@ -230,12 +246,18 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
   const int k_lo = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
   const int* table = block_table + (long long)seq * table_stride;
 
-  // Q tile; rows past n_rows are zero
+  const int tile_first = k_lo / PF_TILE, tile_last = k_hi / PF_TILE;
+  // prologue: Q and the first PF_STAGES-1 key tiles, one commit group per tile
   load_q_rows(sQ, q + (long long)tok0 * q_stride + (long long)h * D, q_stride, n_rows, Q_TILE);
-  const int tile_first = k_lo / KV_TILE, tile_last = k_hi / KV_TILE;
-  load_kv_tile(sKV, sKV + KV_TILE * STRIDE, pool, table, tile_first * KV_TILE, k_lo, k_hi, kvh,
-               n_kv_heads, page_size);
-  cp_async_commit();
+#pragma unroll
+  for (int st = 0; st < PF_STAGES - 1; ++st) {
+    if (tile_first + st <= tile_last) {
+      bf16* dK = sKV + st * STAGE_ELEMS;
+      load_kv_tile<PF_TILE>(dK, dK + PF_TILE * STRIDE, pool, table, (tile_first + st) * PF_TILE,
+                            k_lo, k_hi, kvh, n_kv_heads, page_size);
+    }
+    cp_async_commit();
+  }
 
   float o[D / 8][4];
 #pragma unroll
@@ -244,31 +266,32 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
     for (int e = 0; e < 4; ++e) o[dt][e] = 0.0f;
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
 
+  const int row_lo = warp * 16;
   for (int tile = tile_first; tile <= tile_last; ++tile) {
-    const int stage = (tile - tile_first) & 1;
-    bf16* sK = sKV + stage * 2 * KV_TILE * STRIDE;
-    bf16* sV = sK + KV_TILE * STRIDE;
-    if (tile < tile_last) {
-      bf16* nK = sKV + (stage ^ 1) * 2 * KV_TILE * STRIDE;
-      load_kv_tile(nK, nK + KV_TILE * STRIDE, pool, table, (tile + 1) * KV_TILE, k_lo, k_hi, kvh,
-                   n_kv_heads, page_size);
+    const int it = tile - tile_first;
+    cp_async_wait<PF_STAGES - 2>();  // this tile has landed (one newer group may be in flight)
+    __syncthreads();                 // ... for every thread; and everyone is done with tile-1
+    {                                // refill the stage that tile-1 used
+      const int nt = tile + PF_STAGES - 1;
+      if (nt <= tile_last) {
+        bf16* dK = sKV + ((it + PF_STAGES - 1) % PF_STAGES) * STAGE_ELEMS;
+        load_kv_tile<PF_TILE>(dK, dK + PF_TILE * STRIDE, pool, table, nt * PF_TILE, k_lo, k_hi,
+                              kvh, n_kv_heads, page_size);
+      }
       cp_async_commit();
-      cp_async_wait<1>();
-    } else {
-      cp_async_wait<0>();
     }
-    __syncthreads();
+    const bf16* sK = sKV + (it % PF_STAGES) * STAGE_ELEMS;
+    const bf16* sV = sK + PF_TILE * STRIDE;
 
     // A warp whose 16 rows are all past n_rows, or all before this tile's keys
-    // (causal), still takes part in the barriers but skips the arithmetic.
-    const int row_lo = warp * 16;
-    const bool active = row_lo < n_rows && (pos0 + min(row_lo + 15, n_rows - 1)) >= tile * KV_TILE;
+    // (causal), skips the arithmetic.
+    const bool active = row_lo < n_rows && (pos0 + min(row_lo + 15, n_rows - 1)) >= tile * PF_TILE;
     if (active) {
-      float s[KV_TILE / 8][4];
-      qk_tile<KV_TILE / 8>(s, sQ + row_lo * STRIDE, sK);
-      const int key0 = tile * KV_TILE;
+      float s[PF_TILE / 8][4];
+      qk_tile<PF_TILE / 8>(s, sQ + row_lo * STRIDE, sK);
+      const int key0 = tile * PF_TILE;
 #pragma unroll
-      for (int nt = 0; nt < KV_TILE / 8; ++nt)
+      for (int nt = 0; nt < PF_TILE / 8; ++nt)
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int row = row_lo + (lane >> 2) + 8 * (e >> 1);
@@ -277,10 +300,9 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
           const bool ok = row < n_rows && j <= p && (window <= 0 || j > p - window);
           s[nt][e] = ok ? s[nt][e] * scale_log2 : -INFINITY;
         }
-      softmax_update<KV_TILE / 8>(s, m, l, o);
-      pv_tile<KV_TILE / 8>(o, s, sV);
+      softmax_update<PF_TILE / 8>(s, m, l, o);
+      pv_tile<PF_TILE / 8>(o, s, sV);
     }
-    __syncthreads();  // this stage is refilled by the load issued in the next iteration
   }
 
 #pragma unroll
@@ -299,6 +321,8 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
       }
     }
   }
+  cp_async_wait<0>();  // only empty groups can be pending here
+  }  // which
 }
 
 // -------------------------------------------------------------------- decode
@@ -349,7 +373,7 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
   if (tile_a < tile_b) {
     // Q rows: one per query head of the chunk, the rest zero
     load_q_rows(sQ, q + (long long)tok * q_stride + (long long)head0 * D, D, n_heads_here, 16);
-    load_kv_tile(sKV, sKV + KV_TILE * STRIDE, pool, table, tile_a * KV_TILE, k_lo_all, pos, kvh,
+    load_kv_tile<KV_TILE>(sKV, sKV + KV_TILE * STRIDE, pool, table, tile_a * KV_TILE, k_lo_all, pos, kvh,
                  n_kv_heads, page_size);
     cp_async_commit();
     for (int tile = tile_a; tile < tile_b; ++tile) {
@@ -358,7 +382,7 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
       bf16* sV = sK + KV_TILE * STRIDE;
       if (tile + 1 < tile_b) {
         bf16* nK = sKV + (stage ^ 1) * 2 * KV_TILE * STRIDE;
-        load_kv_tile(nK, nK + KV_TILE * STRIDE, pool, table, (tile + 1) * KV_TILE, k_lo_all, pos,
+        load_kv_tile<KV_TILE>(nK, nK + KV_TILE * STRIDE, pool, table, (tile + 1) * KV_TILE, k_lo_all, pos,
                      kvh, n_kv_heads, page_size);
         cp_async_commit();
         cp_async_wait<1>();
@@ -460,7 +484,8 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_acc,
   }
 }
 
-constexpr size_t PREFILL_SMEM = (size_t)(Q_TILE + 4 * KV_TILE) * STRIDE * sizeof(bf16);
+constexpr size_t PREFILL_SMEM =
+    (size_t)(Q_TILE + PF_STAGES * 2 * PF_TILE) * STRIDE * sizeof(bf16);
 constexpr size_t DECODE_KV_SMEM = (size_t)4 * KV_TILE * STRIDE * sizeof(bf16);
 constexpr size_t DECODE_MERGE_SMEM = (size_t)(2 * 4 * 16 + 4 * 16 * D) * sizeof(float);
 constexpr size_t DECODE_SMEM =
@@ -471,14 +496,17 @@ constexpr size_t DECODE_SMEM =
 
 SI_API int si_attn_head_dim() { return si::D; }
 
-// Attention for the 64-query tiles listed in tile_seq/tile_start.
+// Attention for the 64-query tiles listed in tile_seq/tile_start; tile_pairs holds n_pairs
+// pairs of tile indices (the second may be -1), one pair per block.
 SI_API int si_attn_prefill(const void* q, int q_stride, const void* pool, const int* block_table,
                            int table_stride, const int* cu_q, const int* positions,
-                           const int* tile_seq, const int* tile_start, int n_tiles, void* out,
-                           int out_stride, int n_q_heads, int n_kv_heads, int page_size,
+                           const int* tile_seq, const int* tile_start, const int* tile_pairs,
+                           int n_pairs, void* out, int out_stride, int n_q_heads, int n_kv_heads, int page_size,
                            float scale, int window, cudaStream_t stream) {
-  if (!q || !pool || !block_table || !cu_q || !positions || !tile_seq || !tile_start || !out)
+  if (!q || !pool || !block_table || !cu_q || !positions || !tile_seq || !tile_start ||
+      !tile_pairs || !out)
     return SI_ERR_ARG;
+  const int n_tiles = n_pairs;
   if (n_tiles < 0 || n_q_heads <= 0 || n_kv_heads <= 0 || n_q_heads % n_kv_heads != 0 ||
       page_size <= 0 || table_stride <= 0 || q_stride % 8 != 0 || out_stride % 2 != 0)
     return SI_ERR_ARG;
@@ -495,8 +523,8 @@ SI_API int si_attn_prefill(const void* q, int q_stride, const void* pool, const 
   dim3 grid(n_tiles, n_q_heads);
   SI_LAUNCH(si::attn_prefill_kernel, grid, si::THREADS, si::PREFILL_SMEM, stream,
       (const si::bf16*)q, q_stride, (const si::bf16*)pool, block_table, table_stride, cu_q,
-      positions, tile_seq, tile_start, (si::bf16*)out, out_stride, n_q_heads, n_kv_heads,
-      page_size, scale * si::LOG2E, window);
+      positions, tile_seq, tile_start, tile_pairs, (si::bf16*)out, out_stride, n_q_heads,
+      n_kv_heads, page_size, scale * si::LOG2E, window);
   return SI_OK;
 }
 

@@ -41,6 +41,23 @@ class StepEntry:
     want: list[int] = field(default_factory=list)  # indices into ``tokens``
 
 
+def pair_tiles(work: list[int], out) -> int:
+    """Pair query tiles for the prefill attention kernel: longest with shortest.
+
+    ``work[i]`` is the number of keys tile i attends to.  Writes pairs of tile
+    indices into ``out`` (second index -1 for an odd one out) and returns the
+    number of pairs.  A block runs the two tiles of a pair back to back, so every
+    block of a causal prompt does about the same amount of work.
+    """
+    order = sorted(range(len(work)), key=lambda i: -work[i])
+    n_pairs = (len(order) + 1) // 2
+    for k in range(n_pairs):
+        a, b = order[k], (order[len(order) - 1 - k] if len(order) - 1 - k > k else -1)
+        out[2 * k] = a
+        out[2 * k + 1] = b
+    return n_pairs
+
+
 class Workspace:
     """Named scratch buffers with stable addresses.
 
@@ -96,6 +113,8 @@ class StepContext:
     tile_seq: torch.Tensor
     tile_start: torch.Tensor
     n_tiles: int
+    tile_pairs: torch.Tensor
+    n_pairs: int
     max_kv_len: int
     max_q_len: int
     max_seqs: int
@@ -116,7 +135,7 @@ class BatchBuilder:
         self.max_seq_len = max_seq_len
         self.n_groups = len(cache.groups)
         self.table_len = [pages_for(max_seq_len, g.page_size) for g in cache.groups]
-        self.max_tiles = max_tokens // QUERY_TILE + max_seqs + 1
+        self.max_tiles = (max_tokens // QUERY_TILE + max_seqs + 2) // 2 * 2
 
         off = 0
         self._off: dict[str, tuple[int, int]] = {}
@@ -131,6 +150,7 @@ class BatchBuilder:
         seg("single_seqs", max_seqs)
         seg("tile_seq", self.max_tiles)
         seg("tile_start", self.max_tiles)
+        seg("tile_pairs", self.max_tiles + 1)
         for g in range(self.n_groups):
             seg(f"block_table{g}", max_seqs * self.table_len[g])
         seg("token_ids", max_tokens)
@@ -180,6 +200,8 @@ class BatchBuilder:
         tok_seq = self._h("tok_seq"); logit_rows = self._h("logit_rows")
         single = self._h("single_seqs"); tile_seq = self._h("tile_seq")
         tile_start = self._h("tile_start")
+        tile_pairs = self._h("tile_pairs")
+        tile_work: list[int] = []
         tables = [self._h(f"block_table{g}").reshape(self.max_seqs, self.table_len[g])
                   for g in range(self.n_groups)]
         kv_slots = [self._h(f"kv_slots{g}") for g in range(self.n_groups)]
@@ -217,6 +239,7 @@ class BatchBuilder:
                 for q0 in range(0, n, QUERY_TILE):
                     tile_seq[n_tiles] = s
                     tile_start[n_tiles] = q0
+                    tile_work.append(start + min(q0 + QUERY_TILE, n))  # keys its last row sees
                     n_tiles += 1
             q_lens.append(n); kv_lens.append(end)
             t += n
@@ -234,6 +257,7 @@ class BatchBuilder:
             t += 1
             cu_q[s + 1] = t
         S += pad; N = t
+        n_pairs = pair_tiles(tile_work, tile_pairs)
 
         self.dev.copy_(self.host, non_blocking=True)
         if self._copied is not None:
@@ -251,6 +275,6 @@ class BatchBuilder:
             logit_rows=self._d("logit_rows", r),
             single_seqs=self._d("single_seqs", n_single), n_single=n_single,
             tile_seq=self._d("tile_seq", n_tiles), tile_start=self._d("tile_start", n_tiles),
-            n_tiles=n_tiles, max_kv_len=max(kv_lens) if kv_lens else 0,
+            n_tiles=n_tiles, tile_pairs=self._d("tile_pairs", 2 * n_pairs), n_pairs=n_pairs, max_kv_len=max(kv_lens) if kv_lens else 0,
             max_q_len=max(q_lens) if q_lens else 0, max_seqs=self.max_seqs, ws=ws, q_lens=q_lens, kv_lens=kv_lens,
         )

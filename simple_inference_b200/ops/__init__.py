@@ -303,7 +303,8 @@ def paged_attention(q: torch.Tensor, pool: torch.Tensor, ctx, group: int, out: t
     if ctx.n_tiles:
         _check(lib.si_attn_prefill(
             _p(q), q.stride(0), _p(pool), _p(table), table.stride(0), _p(ctx.cu_q),
-            _p(ctx.positions), _p(ctx.tile_seq), _p(ctx.tile_start), ctx.n_tiles, _p(out),
+            _p(ctx.positions), _p(ctx.tile_seq), _p(ctx.tile_start), _p(ctx.tile_pairs),
+            ctx.n_pairs, _p(out),
             out.stride(0), num_q_heads, num_kv_heads, page_size, _c_float(scale), win, _stream()),
             "attn_prefill")
     if ctx.n_single:

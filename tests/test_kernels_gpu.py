@@ -112,14 +112,17 @@ def paged_case(lens_q, starts, ps, hq, hkv, d, dt, seed=0):
             for q0 in range(0, lens_q[s], 64):
                 tile_seq.append(s)
                 tile_start.append(q0)
-    from simple_inference_b200.engine.batch import Workspace
+    from simple_inference_b200.engine.batch import Workspace, pair_tiles
+    pairs = [0] * (len(tile_seq) + 2)
+    n_pairs = pair_tiles([starts[s] + min(q0 + 64, lens_q[s]) for s, q0 in zip(tile_seq, tile_start)], pairs)
     I = lambda x: torch.tensor(x, dtype=torch.int32, device=dev())  # noqa: E731
     pool = torch.randn(P + 1, 2, hkv, ps, d, device=dev(), generator=g).to(dt)
     qkv = torch.randn(N, (hq + 2 * hkv) * d, device=dev(), generator=g).to(dt)
     ctx = types.SimpleNamespace(
         block_tables=[bt.to(dev())], tok_seq=I(tok_seq), positions=I(pos), cu_q=I(cu),
         kv_slots=[I(slots)], single_seqs=I(single), n_single=len(single), tile_seq=I(tile_seq),
-        tile_start=I(tile_start), n_tiles=len(tile_seq), max_kv_len=max(kv), max_seqs=S,
+        tile_start=I(tile_start), n_tiles=len(tile_seq), tile_pairs=I(pairs[:2 * n_pairs]),
+        n_pairs=n_pairs, max_kv_len=max(kv), max_seqs=S,
         ws=Workspace(dev(), N))
     return qkv, pool, ctx, N
 
