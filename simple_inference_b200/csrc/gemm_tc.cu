@@ -1,0 +1,373 @@
+// bfloat16 matrix product on the fifth-generation tensor cores: out = X W^T with
+// X [M, K] activations and W [N, K] weights (nn.Linear layout), float32
+// accumulation in tensor memory.  It serves every product with many rows
+// (prompt portions); the reference calls cuBLAS for them (F.linear,
+// ops/attention.py:128-130,226; ops/mlp.py:117,128).
+//
+// One persistent block per SM walks over 128 x 256 output tiles.  Roles:
+//   warp 0, one lane   TMA producer: cp.async.bulk.tensor loads of a 128 x 64 tile
+//                      of X and a 256 x 64 tile of W per k-step into a four-stage
+//                      ring of 128-byte-swizzled shared memory; mbarriers with
+//                      expected byte counts say when a stage is full.  Loads are
+//                      plain tiled loads of this GPU's own memory, one per block.
+//   warp 1, one lane   MMA issuer: four tcgen05.mma (M128 N256 K16, kind::f16,
+//                      operands by shared-memory descriptor) per k-step into one
+//                      of two 256-column accumulators in tensor memory;
+//                      tcgen05.commit frees the stage, and after the last k-step
+//                      tells the epilogue that the accumulator is complete.
+//   warps 2..5         epilogue: each warp reads its 32 lanes of the accumulator
+//                      with tcgen05.ld, rounds once to bfloat16 and stores; then
+//                      hands the accumulator back.  With two accumulators the
+//                      epilogue of one tile overlaps the products of the next.
+//
+// Epilogue 2 (SwiGLU): W is the stacked [gate; up] matrix (reference
+// ops/mlp.py:104).  A tile's 256 weight rows are 128 gate rows and the 128 up
+// rows of the same output columns (two TMA boxes), so the epilogue has g and u
+// of an output side by side in tensor memory and writes silu(g) * u (reference
+// ops/mlp.py:125) without ever storing the [M, 2I] intermediate.
+//
+// Every wait on an mbarrier is bounded.  If one runs out, the block records a
+// code in *status, stops issuing work, still meets its final barrier, frees its
+// tensor memory and returns; the host reads *status and raises.
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace si {
+
+typedef __nv_bfloat16 bf16;
+
+constexpr int TC_BM = 128, TC_BN = 256, TC_BK = 64, TC_STAGES = 4;
+constexpr int TC_THREADS = 192;
+constexpr uint32_t TC_A_BYTES = TC_BM * TC_BK * 2;   // 16 KiB
+constexpr uint32_t TC_B_BYTES = TC_BN * TC_BK * 2;   // 32 KiB
+constexpr uint32_t TC_STAGE_BYTES = TC_A_BYTES + TC_B_BYTES;
+constexpr uint32_t TC_TMEM_COLS = 512;               // two accumulators of 256 columns
+constexpr uint32_t TC_SMEM_BYTES = TC_STAGES * TC_STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
+constexpr unsigned long long TC_WAIT_LIMIT_NS = 1000000000ull;  // one second per wait
+
+enum TcStatus { TC_OK = 0, TC_TIMEOUT_PRODUCER = 1, TC_TIMEOUT_MMA = 2, TC_TIMEOUT_EPILOGUE = 3 };
+enum TcEpilogue { TC_EPI_BF16 = 0, TC_EPI_SWIGLU = 2 };
+
+// ------------------------------------------------------------------ PTX helpers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// Bounded wait for the phase with the given parity.  False (and *status set) on time-out.
+__device__ __forceinline__ unsigned long long global_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code) {
+  const unsigned long long t0 = global_ns();
+  for (uint32_t spin = 0;; ++spin) {
+    uint32_t done;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+    if (done) return true;
+    if ((spin & 63u) == 63u && global_ns() - t0 > TC_WAIT_LIMIT_NS) break;
+  }
+  atomicCAS(status, 0, code);
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+// Shared-memory operand descriptor: K-major rows of 128 bytes, 128-byte swizzle, groups of
+// 8 rows 1024 bytes apart (what a TMA box of 64 bfloat16 columns with SWIZZLE_128B writes).
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+  uint64_t d = (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)1 << 16;            // leading byte offset (unused with a swizzle): 16 B
+  d |= (uint64_t)(1024 >> 4) << 32;  // stride byte offset between 8-row groups
+  d |= (uint64_t)1 << 46;            // descriptor version of this architecture
+  d |= (uint64_t)2 << 61;            // SWIZZLE_128B
+  return d;
+}
+// Instruction descriptor: float32 accumulate, bfloat16 A and B, both K-major, N x M.
+__host__ __device__ constexpr uint32_t umma_idesc(int m, int n) {
+  return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b,
+                                          uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
+      ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
+               ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32"
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15,"
+      " %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// ----------------------------------------------------------------------- kernel
+// n_out: output columns (N, or I for SwiGLU).  up_row0: first up row of W (I) for SwiGLU.
+template <int EPI>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+               bf16* __restrict__ out, int ldo, int M, int n_out, int K, int up_row0,
+               int* __restrict__ status) {
+  constexpr int TILE_N_OUT = (EPI == TC_EPI_SWIGLU) ? TC_BN / 2 : TC_BN;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bars = base + TC_STAGES * TC_STAGE_BYTES;
+  // barrier addresses (8 bytes each): full[4], empty[4], acc_full[2], acc_empty[2]; then the TMEM slot
+  const uint32_t full0 = bars, empty0 = bars + 8 * TC_STAGES;
+  const uint32_t acc_full0 = bars + 16 * TC_STAGES, acc_empty0 = acc_full0 + 16;
+  const uint32_t tmem_slot = acc_empty0 + 16;
+  volatile uint32_t* tmem_slot_ptr =
+      reinterpret_cast<volatile uint32_t*>(smem_raw + (tmem_slot - smem_u32(smem_raw)));
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_m = (M + TC_BM - 1) / TC_BM;
+  const int tiles_n = (n_out + TILE_N_OUT - 1) / TILE_N_OUT;
+  const int n_tiles = tiles_m * tiles_n;
+  const int k_blocks = (K + TC_BK - 1) / TC_BK;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < TC_STAGES; ++s) {
+      mbar_init(full0 + 8 * s, 1);
+      mbar_init(empty0 + 8 * s, 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full0 + 8 * b, 1);
+      mbar_init(acc_empty0 + 8 * b, 4);  // one arrival per epilogue warp
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {  // the whole warp allocates tensor memory, and later frees it
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(tmem_slot), "r"(TC_TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    tmem_fence_before();
+  }
+  __syncthreads();
+  tmem_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+
+  if (warp == 0) {
+    if (lane == 0) {  // ---------------------------------------------- TMA producer
+      uint32_t it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x) {
+        const int m0 = (tile % tiles_m) * TC_BM;       // m fastest: neighbours share the W tile
+        const int n0 = (tile / tiles_m) * TILE_N_OUT;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const uint32_t s = it % TC_STAGES, ph = (it / TC_STAGES) & 1u;
+          if (!mbar_wait(empty0 + 8 * s, ph ^ 1u, status, TC_TIMEOUT_PRODUCER)) { ok = false; break; }
+          const uint32_t a_dst = base + s * TC_STAGE_BYTES, b_dst = a_dst + TC_A_BYTES;
+          mbar_expect_tx(full0 + 8 * s, TC_STAGE_BYTES);
+          tma_load_2d(a_dst, &map_x, full0 + 8 * s, kb * TC_BK, m0);
+          if (EPI == TC_EPI_SWIGLU) {
+            tma_load_2d(b_dst, &map_w, full0 + 8 * s, kb * TC_BK, n0);
+            tma_load_2d(b_dst + TC_B_BYTES / 2, &map_w, full0 + 8 * s, kb * TC_BK, up_row0 + n0);
+          } else {
+            tma_load_2d(b_dst, &map_w, full0 + 8 * s, kb * TC_BK, n0);
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {  // ------------------------------------------------ MMA issuer
+      constexpr uint32_t idesc = umma_idesc(TC_BM, TC_BN);
+      uint32_t it = 0, acc_it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x, ++acc_it) {
+        const uint32_t buf = acc_it & 1u, aph = (acc_it >> 1) & 1u;
+        if (!mbar_wait(acc_empty0 + 8 * buf, aph ^ 1u, status, TC_TIMEOUT_MMA)) break;
+        tmem_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * TC_BN;
+        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+          const uint32_t s = it % TC_STAGES, ph = (it / TC_STAGES) & 1u;
+          if (!mbar_wait(full0 + 8 * s, ph, status, TC_TIMEOUT_MMA)) { ok = false; break; }
+          tmem_fence_after();
+          const uint32_t a_src = base + s * TC_STAGE_BYTES;
+          const uint64_t da = umma_desc(a_src), db = umma_desc(a_src + TC_A_BYTES);
+#pragma unroll
+          for (int k = 0; k < TC_BK / 16; ++k)  // 16 columns = 32 bytes further along each row
+            umma_bf16(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+          umma_commit(empty0 + 8 * s);  // the stage is free once these products have read it
+        }
+        if (ok) umma_commit(acc_full0 + 8 * buf);
+      }
+    }
+  } else {  // ------------------------------------------------------------ epilogue
+    const int quarter = warp & 3;  // a warp may read lanes [32*(warp%4), +32) of tensor memory
+    uint32_t acc_it = 0;
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++acc_it) {
+      const uint32_t buf = acc_it & 1u, aph = (acc_it >> 1) & 1u;
+      if (!mbar_wait(acc_full0 + 8 * buf, aph, status, TC_TIMEOUT_EPILOGUE)) break;
+      tmem_fence_after();
+      const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * TILE_N_OUT;
+      const int row = m0 + quarter * 32 + lane;
+      const uint32_t taddr = tmem_base + buf * TC_BN + ((uint32_t)(quarter * 32) << 16);
+      bf16* orow = out + (size_t)row * ldo + n0;
+#pragma unroll 1
+      for (int c = 0; c < TILE_N_OUT / 32; ++c) {
+        uint32_t g[32];
+        float v[32];
+        tmem_ld32(taddr + c * 32, g);
+        if (EPI == TC_EPI_SWIGLU) {
+          uint32_t u[32];
+          tmem_ld32(taddr + TC_BN / 2 + c * 32, u);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const float gi = __uint_as_float(g[i]);
+            v[i] = (gi / (1.0f + expf(-gi))) * __uint_as_float(u[i]);
+          }
+        } else {
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(g[i]);
+        }
+        if (row < M) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const int col = n0 + c * 32 + j * 8;
+            if (col < n_out) {  // n_out is a multiple of 8
+              float w8[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) w8[i] = v[j * 8 + i];
+              store8<bf16>(orow + c * 32 + j * 8, w8);
+            }
+          }
+        }
+      }
+      tmem_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty0 + 8 * buf);
+    }
+  }
+
+  tmem_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tmem_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;"
+                 ::"r"(tmem_base), "r"(TC_TMEM_COLS) : "memory");
+  }
+}
+
+// ------------------------------------------------------------------------- host
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// rows x cols bfloat16 matrix with `ld` elements between rows; boxes of box_rows x 64 columns
+static bool make_map(CUtensorMap* map, const void* ptr, int rows, int cols, int ld, int box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * sizeof(bf16)};
+  cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows};
+  cuuint32_t elem[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box,
+            elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace si
+
+// out[M, N] = X[M, K] W[N, K]^T in bfloat16 (epilogue 0), or out[M, N] = silu(X Wg^T) * (X Wu^T)
+// with W = [Wg; Wu] of 2N rows (epilogue 2).  K and N multiples of 8, ldx and ldo multiples of 8,
+// all pointers 16-byte aligned.  status: one int in device memory, 0 while all is well.
+SI_API int si_gemm_tc_bf16(const void* X, int ldx, const void* W, void* out, int ldo, int M, int N,
+                           int K, int epilogue, int* status, cudaStream_t stream) {
+  using namespace si;
+  if (!X || !W || !out || !status || M < 0 || N <= 0 || K <= 0 || ldx < K || ldo < N)
+    return SI_ERR_ARG;
+  if (K % 8 != 0 || N % 8 != 0 || ldx % 8 != 0 || ldo % 8 != 0) return SI_ERR_UNSUPPORTED;
+  if (((uintptr_t)X | (uintptr_t)W | (uintptr_t)out) & 15) return SI_ERR_ARG;
+  if (epilogue != TC_EPI_BF16 && epilogue != TC_EPI_SWIGLU) return SI_ERR_ARG;
+  if (M == 0) return SI_OK;
+  const bool swiglu = epilogue == TC_EPI_SWIGLU;
+  CUtensorMap map_x, map_w;
+  if (!make_map(&map_x, X, M, K, ldx, TC_BM)) return SI_ERR_UNSUPPORTED;
+  if (!make_map(&map_w, W, swiglu ? 2 * N : N, K, K, swiglu ? TC_BN / 2 : TC_BN))
+    return SI_ERR_UNSUPPORTED;
+  static int n_sms = 0;
+  if (n_sms == 0) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e == cudaSuccess) e = cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return (int)e;
+  }
+  const int tile_n = swiglu ? TC_BN / 2 : TC_BN;
+  const int n_tiles = ((M + TC_BM - 1) / TC_BM) * ((N + tile_n - 1) / tile_n);
+  const int grid = n_tiles < n_sms ? n_tiles : n_sms;
+  if (swiglu) {
+    static bool configured = false;
+    if (!configured) {
+      cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<TC_EPI_SWIGLU>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES);
+      if (e != cudaSuccess) return (int)e;
+      configured = true;
+    }
+    SI_LAUNCH(gemm_tc_kernel<TC_EPI_SWIGLU>, grid, TC_THREADS, TC_SMEM_BYTES, stream, map_x, map_w,
+              (bf16*)out, ldo, M, N, K, N, status);
+  } else {
+    static bool configured = false;
+    if (!configured) {
+      cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<TC_EPI_BF16>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES);
+      if (e != cudaSuccess) return (int)e;
+      configured = true;
+    }
+    SI_LAUNCH(gemm_tc_kernel<TC_EPI_BF16>, grid, TC_THREADS, TC_SMEM_BYTES, stream, map_x, map_w,
+              (bf16*)out, ldo, M, N, K, 0, status);
+  }
+  return SI_OK;
+}

@@ -19,7 +19,7 @@ import torch
 
 from .build import KernelBuildError, load_library
 
-_CORE_SOURCES = ["rowwise.cu", "rope_kv.cu", "gemm_fp32.cu", "gemm_skinny.cu",
+_CORE_SOURCES = ["rowwise.cu", "rope_kv.cu", "gemm_fp32.cu", "gemm_skinny.cu", "gemm_tc.cu",
                  "attention_generic.cu", "sampling.cu"]
 
 _ERRORS = {
@@ -149,6 +149,49 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
 # ------------------------------------------------------------ matrix product
 
 SKINNY_MAX_ROWS = 16  # up to this many tokens the hand-written weight-streaming product runs
+TENSOR_CORE_MIN_ROWS = 96  # from this many tokens the tcgen05 product runs (its tiles have 128 rows)
+
+_status: dict[int, torch.Tensor] = {}  # per device: one int the tcgen05 kernels write on a time-out
+_STATUS_TEXT = {1: "the TMA producer", 2: "the MMA issuer", 3: "the epilogue"}
+
+
+def status_tensor(device: torch.device) -> torch.Tensor:
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    if idx not in _status:
+        _status[idx] = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", idx))
+    return _status[idx]
+
+
+def check_status(device: torch.device | None = None) -> None:
+    """Raise if a tcgen05 kernel gave up waiting on a barrier (synchronises the device)."""
+    for idx, t in list(_status.items()):
+        if device is not None and device.index not in (None, idx):
+            continue
+        code = int(t.item())
+        if code != 0:
+            t.zero_()
+            raise KernelError(f"tcgen05 matrix product on cuda:{idx}: {_STATUS_TEXT.get(code, code)} "
+                              f"waited over a second for a barrier and gave up; results are invalid")
+
+
+def _tc_ok(x: torch.Tensor, weight: torch.Tensor, n_out: int) -> bool:
+    return (x.is_cuda and x.dtype == torch.bfloat16 and x.shape[0] >= TENSOR_CORE_MIN_ROWS
+            and x.shape[1] % 8 == 0 and n_out % 8 == 0 and x.stride(0) % 8 == 0
+            and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
+
+
+def linear_tc(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, swiglu: bool = False) -> torch.Tensor:
+    """The tcgen05 product: ``out = x @ weight.T`` (bfloat16), or its SwiGLU form."""
+    _dev(x, weight, out)
+    m, k = x.shape
+    n = out.shape[1]
+    if out.dtype != torch.bfloat16 or out.shape[0] != m or weight.shape != ((2 * n if swiglu else n), k) \
+            or out.stride(0) % 8 != 0 or out.data_ptr() % 16 != 0:
+        raise KernelError("linear_tc: operands do not fit")
+    _check(core().si_gemm_tc_bf16(_p(x), x.stride(0), _p(weight), _p(out), out.stride(0), m, n, k,
+                                  2 if swiglu else 0, _p(status_tensor(x.device)), _stream()),
+           "gemm_tc")
+    return out
 
 
 def _skinny_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
