@@ -31,18 +31,22 @@
 // tensor memory and returns; the host reads *status and raises.
 #include <cuda.h>
 
+#include <functional>
+#include <mutex>
+#include <unordered_map>
+
 #include "common.cuh"
 
 namespace si {
 
 typedef __nv_bfloat16 bf16;
 
-constexpr int TC_BM = 128, TC_BN = 256, TC_BK = 64, TC_STAGES = 4;
+constexpr int TC_BM = 128, TC_BN_MAX = 256, TC_BK = 64, TC_STAGES = 4;
 constexpr int TC_THREADS = 192;
-constexpr uint32_t TC_A_BYTES = TC_BM * TC_BK * 2;   // 16 KiB
-constexpr uint32_t TC_B_BYTES = TC_BN * TC_BK * 2;   // 32 KiB
+constexpr uint32_t TC_A_BYTES = TC_BM * TC_BK * 2;       // 16 KiB
+constexpr uint32_t TC_B_BYTES = TC_BN_MAX * TC_BK * 2;   // 32 KiB reserved; a narrower tile fills less
 constexpr uint32_t TC_STAGE_BYTES = TC_A_BYTES + TC_B_BYTES;
-constexpr uint32_t TC_TMEM_COLS = 512;               // two accumulators of 256 columns
+constexpr uint32_t TC_TMEM_COLS = 512;                   // two accumulators of up to 256 columns
 constexpr uint32_t TC_SMEM_BYTES = TC_STAGES * TC_STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
 constexpr unsigned long long TC_WAIT_LIMIT_NS = 1000000000ull;  // one second per wait
 
@@ -141,12 +145,14 @@ __device__ __forceinline__ void tmem_ld_wait() {
 
 // ----------------------------------------------------------------------- kernel
 // n_out: output columns (N, or I for SwiGLU).  up_row0: first up row of W (I) for SwiGLU.
-template <int EPI>
+// BN: weight rows (accumulator columns) per tile, a multiple of 32 up to 256.
+template <int EPI, int BN>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                bf16* __restrict__ out, int ldo, int M, int n_out, int K, int up_row0,
                int* __restrict__ status) {
-  constexpr int TILE_N_OUT = (EPI == TC_EPI_SWIGLU) ? TC_BN / 2 : TC_BN;
+  constexpr int TILE_N_OUT = (EPI == TC_EPI_SWIGLU) ? BN / 2 : BN;
+  constexpr uint32_t STAGE_TX_BYTES = TC_A_BYTES + BN * TC_BK * 2;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t bars = base + TC_STAGES * TC_STAGE_BYTES;
@@ -195,11 +201,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
           const uint32_t s = it % TC_STAGES, ph = (it / TC_STAGES) & 1u;
           if (!mbar_wait(empty0 + 8 * s, ph ^ 1u, status, TC_TIMEOUT_PRODUCER)) { ok = false; break; }
           const uint32_t a_dst = base + s * TC_STAGE_BYTES, b_dst = a_dst + TC_A_BYTES;
-          mbar_expect_tx(full0 + 8 * s, TC_STAGE_BYTES);
+          mbar_expect_tx(full0 + 8 * s, STAGE_TX_BYTES);
           tma_load_2d(a_dst, &map_x, full0 + 8 * s, kb * TC_BK, m0);
           if (EPI == TC_EPI_SWIGLU) {
             tma_load_2d(b_dst, &map_w, full0 + 8 * s, kb * TC_BK, n0);
-            tma_load_2d(b_dst + TC_B_BYTES / 2, &map_w, full0 + 8 * s, kb * TC_BK, up_row0 + n0);
+            tma_load_2d(b_dst + BN * TC_BK, &map_w, full0 + 8 * s, kb * TC_BK, up_row0 + n0);
           } else {
             tma_load_2d(b_dst, &map_w, full0 + 8 * s, kb * TC_BK, n0);
           }
@@ -208,14 +214,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     }
   } else if (warp == 1) {
     if (lane == 0) {  // ------------------------------------------------ MMA issuer
-      constexpr uint32_t idesc = umma_idesc(TC_BM, TC_BN);
+      constexpr uint32_t idesc = umma_idesc(TC_BM, BN);
       uint32_t it = 0, acc_it = 0;
       bool ok = true;
       for (int tile = blockIdx.x; ok && tile < n_tiles; tile += gridDim.x, ++acc_it) {
         const uint32_t buf = acc_it & 1u, aph = (acc_it >> 1) & 1u;
         if (!mbar_wait(acc_empty0 + 8 * buf, aph ^ 1u, status, TC_TIMEOUT_MMA)) break;
         tmem_fence_after();
-        const uint32_t d_tmem = tmem_base + buf * TC_BN;
+        const uint32_t d_tmem = tmem_base + buf * TC_BN_MAX;
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const uint32_t s = it % TC_STAGES, ph = (it / TC_STAGES) & 1u;
           if (!mbar_wait(full0 + 8 * s, ph, status, TC_TIMEOUT_MMA)) { ok = false; break; }
@@ -239,7 +245,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       tmem_fence_after();
       const int m0 = (tile % tiles_m) * TC_BM, n0 = (tile / tiles_m) * TILE_N_OUT;
       const int row = m0 + quarter * 32 + lane;
-      const uint32_t taddr = tmem_base + buf * TC_BN + ((uint32_t)(quarter * 32) << 16);
+      const uint32_t taddr = tmem_base + buf * TC_BN_MAX + ((uint32_t)(quarter * 32) << 16);
       bf16* orow = out + (size_t)row * ldo + n0;
 #pragma unroll 1
       for (int c = 0; c < TILE_N_OUT / 32; ++c) {
@@ -248,7 +254,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         tmem_ld32(taddr + c * 32, g);
         if (EPI == TC_EPI_SWIGLU) {
           uint32_t u[32];
-          tmem_ld32(taddr + TC_BN / 2 + c * 32, u);
+          tmem_ld32(taddr + BN / 2 + c * 32, u);
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
@@ -306,17 +312,87 @@ static EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
-// rows x cols bfloat16 matrix with `ld` elements between rows; boxes of box_rows x 64 columns
+// rows x cols bfloat16 matrix with `ld` elements between rows; boxes of box_rows x 64 columns.
+// Encoding a map costs tens of microseconds of host time, and a step asks for the same few
+// (pointer, shape) combinations again and again, so the encoded maps are kept.
+struct MapKey {
+  const void* ptr;
+  int rows, cols, ld, box_rows;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = std::hash<const void*>()(k.ptr);
+    for (int v : {k.rows, k.cols, k.ld, k.box_rows}) h = h * 1000003u + (size_t)v;
+    return h;
+  }
+};
+static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
+static std::mutex g_maps_mutex;
+
 static bool make_map(CUtensorMap* map, const void* ptr, int rows, int cols, int ld, int box_rows) {
+  const MapKey key{ptr, rows, cols, ld, box_rows};
+  std::lock_guard<std::mutex> lock(g_maps_mutex);
+  auto it = g_maps.find(key);
+  if (it != g_maps.end()) {
+    *map = it->second;
+    return true;
+  }
   EncodeTiledFn fn = encode_tiled_fn();
   if (!fn) return false;
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)ld * sizeof(bf16)};
   cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows};
   cuuint32_t elem[2] = {1, 1};
-  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box,
-            elem, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  if (fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return false;
+  if (g_maps.size() > 4096) g_maps.clear();
+  g_maps.emplace(key, *map);
+  return true;
+}
+
+// Tile width for an [M, N] output on n_sms persistent blocks: the widest tile is the most
+// efficient per tile, but the blocks finish together only if the tile count divides well.
+// Score = (mean tiles per block / most tiles of a block) * a mild preference for wide tiles.
+static int choose_bn(int M, int N, int n_sms) {
+  const int tiles_m = (M + TC_BM - 1) / TC_BM;
+  int best = 256;
+  double best_score = -1.0;
+  for (int bn : {256, 224, 192, 160, 128}) {
+    const long long tiles = (long long)tiles_m * ((N + bn - 1) / bn);
+    const long long per_block = (tiles + n_sms - 1) / n_sms;
+    const double balance = (double)tiles / ((double)per_block * n_sms);
+    const double used = (double)N / ((double)((N + bn - 1) / bn) * bn);  // part of the tiles inside N
+    const double width = bn >= 224 ? 1.0 : (bn == 192 ? 0.97 : (bn == 160 ? 0.93 : 0.88));
+    const double score = balance * used * width;
+    if (score > best_score + 1e-9) {
+      best_score = score;
+      best = bn;
+    }
+  }
+  return best;
+}
+
+template <int EPI, int BN>
+static int launch_tc(const CUtensorMap& map_x, const CUtensorMap& map_w, bf16* out, int ldo, int M,
+                     int N, int K, int up_row0, int* status, int n_sms, cudaStream_t stream) {
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<EPI, BN>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  constexpr int tile_n = EPI == TC_EPI_SWIGLU ? BN / 2 : BN;
+  const int n_tiles = ((M + TC_BM - 1) / TC_BM) * ((N + tile_n - 1) / tile_n);
+  const int grid = n_tiles < n_sms ? n_tiles : n_sms;
+  SI_LAUNCH((gemm_tc_kernel<EPI, BN>), grid, TC_THREADS, TC_SMEM_BYTES, stream, map_x, map_w, out,
+            ldo, M, N, K, up_row0, status);
+  return SI_OK;
 }
 
 }  // namespace si
@@ -333,11 +409,6 @@ SI_API int si_gemm_tc_bf16(const void* X, int ldx, const void* W, void* out, int
   if (((uintptr_t)X | (uintptr_t)W | (uintptr_t)out) & 15) return SI_ERR_ARG;
   if (epilogue != TC_EPI_BF16 && epilogue != TC_EPI_SWIGLU) return SI_ERR_ARG;
   if (M == 0) return SI_OK;
-  const bool swiglu = epilogue == TC_EPI_SWIGLU;
-  CUtensorMap map_x, map_w;
-  if (!make_map(&map_x, X, M, K, ldx, TC_BM)) return SI_ERR_UNSUPPORTED;
-  if (!make_map(&map_w, W, swiglu ? 2 * N : N, K, K, swiglu ? TC_BN / 2 : TC_BN))
-    return SI_ERR_UNSUPPORTED;
   static int n_sms = 0;
   if (n_sms == 0) {
     int dev = 0;
@@ -345,29 +416,20 @@ SI_API int si_gemm_tc_bf16(const void* X, int ldx, const void* W, void* out, int
     if (e == cudaSuccess) e = cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev);
     if (e != cudaSuccess) return (int)e;
   }
-  const int tile_n = swiglu ? TC_BN / 2 : TC_BN;
-  const int n_tiles = ((M + TC_BM - 1) / TC_BM) * ((N + tile_n - 1) / tile_n);
-  const int grid = n_tiles < n_sms ? n_tiles : n_sms;
-  if (swiglu) {
-    static bool configured = false;
-    if (!configured) {
-      cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<TC_EPI_SWIGLU>,
-                                           cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES);
-      if (e != cudaSuccess) return (int)e;
-      configured = true;
-    }
-    SI_LAUNCH(gemm_tc_kernel<TC_EPI_SWIGLU>, grid, TC_THREADS, TC_SMEM_BYTES, stream, map_x, map_w,
-              (bf16*)out, ldo, M, N, K, N, status);
-  } else {
-    static bool configured = false;
-    if (!configured) {
-      cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<TC_EPI_BF16>,
-                                           cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES);
-      if (e != cudaSuccess) return (int)e;
-      configured = true;
-    }
-    SI_LAUNCH(gemm_tc_kernel<TC_EPI_BF16>, grid, TC_THREADS, TC_SMEM_BYTES, stream, map_x, map_w,
-              (bf16*)out, ldo, M, N, K, 0, status);
+  CUtensorMap map_x, map_w;
+  if (!make_map(&map_x, X, M, K, ldx, TC_BM)) return SI_ERR_UNSUPPORTED;
+  if (epilogue == TC_EPI_SWIGLU) {
+    if (!make_map(&map_w, W, 2 * N, K, K, 128)) return SI_ERR_UNSUPPORTED;
+    return launch_tc<TC_EPI_SWIGLU, 256>(map_x, map_w, (bf16*)out, ldo, M, N, K, N, status, n_sms,
+                                         stream);
   }
-  return SI_OK;
+  const int bn = choose_bn(M, N, n_sms);
+  if (!make_map(&map_w, W, N, K, K, bn)) return SI_ERR_UNSUPPORTED;
+  switch (bn) {
+    case 256: return launch_tc<TC_EPI_BF16, 256>(map_x, map_w, (bf16*)out, ldo, M, N, K, 0, status, n_sms, stream);
+    case 224: return launch_tc<TC_EPI_BF16, 224>(map_x, map_w, (bf16*)out, ldo, M, N, K, 0, status, n_sms, stream);
+    case 192: return launch_tc<TC_EPI_BF16, 192>(map_x, map_w, (bf16*)out, ldo, M, N, K, 0, status, n_sms, stream);
+    case 160: return launch_tc<TC_EPI_BF16, 160>(map_x, map_w, (bf16*)out, ldo, M, N, K, 0, status, n_sms, stream);
+    default: return launch_tc<TC_EPI_BF16, 128>(map_x, map_w, (bf16*)out, ldo, M, N, K, 0, status, n_sms, stream);
+  }
 }

@@ -41,17 +41,30 @@ def core_sources() -> list[str]:
     return [s for s in _CORE_SOURCES if (CSRC / s).is_file()]
 
 
+_core_lib: ctypes.CDLL | None = None
+_attention_libs: dict[int, ctypes.CDLL] = {}
+
+
 def core() -> ctypes.CDLL:
-    return load_library("si_core", core_sources())
+    """The library of all kernels that do not depend on the head size (built at first use)."""
+    global _core_lib
+    if _core_lib is None:
+        _core_lib = load_library("si_core", core_sources())
+    return _core_lib
 
 
 def attention_library(head_dim: int) -> ctypes.CDLL:
     """Tensor-core attention kernels are compiled for one head size at a time."""
-    if head_dim % 16 != 0 or not (16 <= head_dim <= 256):
-        raise KernelError(
-            f"head_dim {head_dim}: the attention kernels take multiples of 16 from 16 to 256"
-        )
-    return load_library(f"si_attn_d{head_dim}", ["attention_mma.cu"], [f"-DSI_HEAD_DIM={head_dim}"])
+    lib = _attention_libs.get(head_dim)
+    if lib is None:
+        if head_dim % 16 != 0 or not (16 <= head_dim <= 256):
+            raise KernelError(
+                f"head_dim {head_dim}: the attention kernels take multiples of 16 from 16 to 256"
+            )
+        lib = load_library(f"si_attn_d{head_dim}", ["attention_mma.cu"],
+                           [f"-DSI_HEAD_DIM={head_dim}"])
+        _attention_libs[head_dim] = lib
+    return lib
 
 
 launch_count = 0  # kernels of this package launched so far (a graph replay is counted by its owner)
@@ -203,9 +216,10 @@ def _skinny_ok(x: torch.Tensor, weight: torch.Tensor) -> bool:
 def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
     """``out = x @ weight.T`` for ``weight`` in the ``[out, in]`` layout.
 
-    float32 operands: the FMA kernel (true 32-bit).  bfloat16 operands: for up
-    to 16 rows the weight-streaming tensor-core kernel, above that the library
-    GEMM; float32 accumulation either way; ``out`` may be bfloat16 or float32.
+    float32 operands: the FMA kernel (true 32-bit).  bfloat16 operands: up to 16
+    rows the weight-streaming kernel, from 96 rows the tcgen05 kernel, between
+    them (and for float32 output above 16 rows) the library GEMM; float32
+    accumulation in every case; ``out`` may be bfloat16 or float32.
     """
     _dev(x, weight, out)
     m, k = x.shape
@@ -222,6 +236,8 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> torch.Te
         _check(core().si_gemm_skinny_bf16(_p(x), x.stride(0), _p(weight), _p(out), out.stride(0),
                                           m, n, k, 0 if out.dtype == torch.bfloat16 else 1,
                                           _stream()), "gemm_skinny")
+    elif out.dtype == torch.bfloat16 and _tc_ok(x, weight, n) and out.stride(0) % 8 == 0:
+        linear_tc(x, weight, out)
     elif out.dtype == torch.bfloat16:
         torch.mm(x, weight.t(), out=out)
     else:
@@ -230,8 +246,9 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> torch.Te
 
 
 def can_fuse_swiglu(x: torch.Tensor, weight: torch.Tensor) -> bool:
-    """Whether ``linear_swiglu`` can run for these operands (few bfloat16 rows on the GPU)."""
-    return _skinny_ok(x, weight)
+    """Whether ``linear_swiglu`` can run for these operands: bfloat16 on the GPU, and either
+    few rows (weight-streaming kernel) or many (tcgen05 kernel)."""
+    return _skinny_ok(x, weight) or _tc_ok(x, weight, weight.shape[0] // 2)
 
 
 def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
@@ -240,8 +257,10 @@ def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor, out: torch.Tensor) -
     m, k = x.shape
     inter = out.shape[1]
     if w_gate_up.shape != (2 * inter, k) or out.shape[0] != m or out.dtype != torch.bfloat16 \
-            or not _skinny_ok(x, w_gate_up):
+            or not can_fuse_swiglu(x, w_gate_up):
         raise KernelError("linear_swiglu: operands do not fit (see can_fuse_swiglu)")
+    if not _skinny_ok(x, w_gate_up):
+        return linear_tc(x, w_gate_up, out, swiglu=True)
     _check(core().si_gemm_skinny_bf16(_p(x), x.stride(0), _p(w_gate_up), _p(out), out.stride(0),
                                       m, inter, k, 2, _stream()), "gemm_skinny_swiglu")
     return out
@@ -387,5 +406,6 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
     return out
 
 
-__all__ = ["KernelError", "KernelBuildError", "embed_gather", "rmsnorm", "swiglu", "linear", "linear_swiglu", "can_fuse_swiglu",
+__all__ = ["KernelError", "KernelBuildError", "embed_gather", "rmsnorm", "swiglu", "linear", "linear_swiglu", "linear_tc",
+           "can_fuse_swiglu", "check_status", "status_tensor",
            "rope_kv_store", "attention_generic", "paged_attention", "plan_kv_splits", "sample", "core", "attention_library"]

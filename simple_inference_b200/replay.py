@@ -24,6 +24,7 @@ from pathlib import Path
 import numpy as np
 import torch
 
+from . import ops
 from .cache.manager import CacheManager
 from .engine.batch import StepEntry
 from .engine.runner import ModelRunner
@@ -113,6 +114,7 @@ def main(argv: list[str] | None = None) -> int:
             for batch in _split(entries, cap):
                 logits = runner.step(batch)
                 host = logits.cpu().numpy() if logits.shape[0] else None
+                ops.check_status(rt.device)
                 r = 0
                 for b in batch:
                     base = consumed[b.request]

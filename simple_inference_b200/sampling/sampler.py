@@ -27,6 +27,7 @@ class Sampler:
         self._dev = torch.zeros(_FIELDS * max_rows, dtype=torch.int32, device=device)
         self._out = torch.zeros(max_rows, dtype=torch.int32, device=device)
         self._out_host = torch.zeros(max_rows, dtype=torch.int32, pin_memory=pin)
+        self._status_host = torch.zeros(1, dtype=torch.int32, pin_memory=pin)
 
     def _field(self, buf, i: int, n: int):
         return buf[i * self.max_rows: i * self.max_rows + n]
@@ -58,5 +59,10 @@ class Sampler:
                    self._field(d, 4, n), self._field(d, 5, n), self._out[:n])
         self._out_host[:n].copy_(self._out[:n], non_blocking=True)
         if self.device.type == "cuda":
+            # the kernels' status word rides home with the tokens: one synchronisation for both
+            status = ops.status_tensor(self.device)
+            self._status_host.copy_(status, non_blocking=True)
             torch.cuda.current_stream().synchronize()
+            if int(self._status_host[0]) != 0:
+                ops.check_status(self.device)
         return self._out_host[:n].tolist()

@@ -289,3 +289,30 @@ def test_weight_streaming_product_for_few_rows(ops, m, n, k):
     one = torch.empty(1, 2 * n, device=dev())
     ops.linear(x[m - 1:m], w, one)
     assert torch.equal(one[0], out32[m - 1])
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (130, 264, 72), (96, 40, 8), (300, 5120, 3072),
+                                   (2048, 3072, 8192), (1000, 331 * 8, 120)])
+def test_tensor_memory_product_for_many_rows(ops, m, n, k):
+    """The tcgen05 product that prompt portions use (M >= 96): TMA loads, accumulators in
+    tensor memory; plain and SwiGLU epilogues; ragged edges in every dimension."""
+    g = gen(8)
+    x = (torch.randn(m, k, device=dev(), generator=g) * 0.5).bfloat16()
+    w = (torch.randn(2 * n, k, device=dev(), generator=g) * 0.1).bfloat16()
+    ref = x.float() @ w.float().T
+    out = torch.zeros(m, 2 * n, device=dev(), dtype=torch.bfloat16)
+    ops.linear(x, w, out)                                   # routed to the tcgen05 kernel
+    ops.check_status()
+    assert (out.float() - ref).abs().max() < 8e-3 * max(1.0, float(ref.abs().max()))
+    fused = torch.zeros(m, n, device=dev(), dtype=torch.bfloat16)
+    assert ops.can_fuse_swiglu(x, w)
+    ops.linear_swiglu(x, w, fused)
+    ops.check_status()
+    gate, up = ref[:, :n], ref[:, n:]
+    want = gate * torch.sigmoid(gate) * up
+    assert (fused.float() - want).abs().max() < 8e-3 * max(1.0, float(want.abs().max()))
+    # a row's result does not depend on how many rows ride along (same k order for every tile)
+    half = torch.zeros(m - 32, 2 * n, device=dev(), dtype=torch.bfloat16)
+    ops.linear(x[32:].contiguous(), w, half) if m - 32 >= 96 else None
+    if m - 32 >= 96:
+        assert torch.equal(half, out[32:])
