@@ -139,13 +139,22 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr) : "memory");
 }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32"
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr) : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
 // ----------------------------------------------------------------------- kernel
 // n_out: output columns (N, or I for SwiGLU).  up_row0: first up row of W (I) for SwiGLU.
-// BN: weight rows (accumulator columns) per tile, a multiple of 32 up to 256.
+// BN: weight rows (accumulator columns) per tile, a multiple of 16 up to 256.
 template <int EPI, int BN>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
@@ -247,13 +256,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       const int row = m0 + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + buf * TC_BN_MAX + ((uint32_t)(quarter * 32) << 16);
       bf16* orow = out + (size_t)row * ldo + n0;
+      if (EPI == TC_EPI_SWIGLU) {
 #pragma unroll 1
-      for (int c = 0; c < TILE_N_OUT / 32; ++c) {
-        uint32_t g[32];
-        float v[32];
-        tmem_ld32(taddr + c * 32, g);
-        if (EPI == TC_EPI_SWIGLU) {
-          uint32_t u[32];
+        for (int c = 0; c < TILE_N_OUT / 32; ++c) {
+          uint32_t g[32], u[32];
+          float v[32];
+          tmem_ld32(taddr + c * 32, g);
           tmem_ld32(taddr + BN / 2 + c * 32, u);
           tmem_ld_wait();
 #pragma unroll
@@ -261,20 +269,55 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             const float gi = __uint_as_float(g[i]);
             v[i] = (gi / (1.0f + expf(-gi))) * __uint_as_float(u[i]);
           }
-        } else {
-          tmem_ld_wait();
+          if (row < M) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(g[i]);
+            for (int j = 0; j < 4; ++j) {
+              const int col = n0 + c * 32 + j * 8;
+              if (col < n_out) {  // n_out is a multiple of 8
+                float w8[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) w8[i] = v[j * 8 + i];
+                store8<bf16>(orow + c * 32 + j * 8, w8);
+              }
+            }
+          }
         }
-        if (row < M) {
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < TILE_N_OUT / 32; ++c) {  // two 16-column loads in flight per turn
+          uint32_t a[16], b[16];
+          tmem_ld16(taddr + c * 32, a);
+          tmem_ld16(taddr + c * 32 + 16, b);
+          tmem_ld_wait();
+          if (row < M) {
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const int col = n0 + c * 32 + j * 8;
-            if (col < n_out) {  // n_out is a multiple of 8
-              float w8[8];
+            for (int j = 0; j < 4; ++j) {
+              const int col = n0 + c * 32 + j * 8;
+              if (col < n_out) {
+                float w8[8];
 #pragma unroll
-              for (int i = 0; i < 8; ++i) w8[i] = v[j * 8 + i];
-              store8<bf16>(orow + c * 32 + j * 8, w8);
+                for (int i = 0; i < 8; ++i)
+                  w8[i] = __uint_as_float(j < 2 ? a[j * 8 + i] : b[(j - 2) * 8 + i]);
+                store8<bf16>(orow + c * 32 + j * 8, w8);
+              }
+            }
+          }
+        }
+        if (TILE_N_OUT % 32 != 0) {  // a last half-width chunk of 16 columns
+          constexpr int c0 = TILE_N_OUT / 32 * 32;
+          uint32_t a[16];
+          tmem_ld16(taddr + c0, a);
+          tmem_ld_wait();
+          if (row < M) {
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+              const int col = n0 + c0 + j * 8;
+              if (col < n_out) {
+                float w8[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) w8[i] = __uint_as_float(a[j * 8 + i]);
+                store8<bf16>(orow + c0 + j * 8, w8);
+              }
             }
           }
         }
@@ -362,12 +405,13 @@ static int choose_bn(int M, int N, int n_sms) {
   const int tiles_m = (M + TC_BM - 1) / TC_BM;
   int best = 256;
   double best_score = -1.0;
-  for (int bn : {256, 224, 192, 160, 128}) {
+  for (int bn = 256; bn >= 128; bn -= 16) {
     const long long tiles = (long long)tiles_m * ((N + bn - 1) / bn);
     const long long per_block = (tiles + n_sms - 1) / n_sms;
     const double balance = (double)tiles / ((double)per_block * n_sms);
     const double used = (double)N / ((double)((N + bn - 1) / bn) * bn);  // part of the tiles inside N
-    const double width = bn >= 224 ? 1.0 : (bn == 192 ? 0.97 : (bn == 160 ? 0.93 : 0.88));
+    // a narrower tile re-reads X more often per product: about 1% per 16 columns below 256
+    const double width = 1.0 - 0.01 * (256 - bn) / 16;
     const double score = balance * used * width;
     if (score > best_score + 1e-9) {
       best_score = score;
@@ -425,11 +469,22 @@ SI_API int si_gemm_tc_bf16(const void* X, int ldx, const void* W, void* out, int
   }
   const int bn = choose_bn(M, N, n_sms);
   if (!make_map(&map_w, W, N, K, K, bn)) return SI_ERR_UNSUPPORTED;
+#define SI_TC_CASE(W)                                                                         \
+  case W:                                                                                     \
+    return launch_tc<TC_EPI_BF16, W>(map_x, map_w, (bf16*)out, ldo, M, N, K, 0, status, n_sms, \
+                                     stream)
   switch (bn) {
-    case 256: return launch_tc<TC_EPI_BF16, 256>(map_x, map_w, (bf16*)out, ldo, M, N, K, 0, status, n_sms, stream);
-    case 224: return launch_tc<TC_EPI_BF16, 224>(map_x, map_w, (bf16*)out, ldo, M, N, K, 0, status, n_sms, stream);
-    case 192: return launch_tc<TC_EPI_BF16, 192>(map_x, map_w, (bf16*)out, ldo, M, N, K, 0, status, n_sms, stream);
-    case 160: return launch_tc<TC_EPI_BF16, 160>(map_x, map_w, (bf16*)out, ldo, M, N, K, 0, status, n_sms, stream);
-    default: return launch_tc<TC_EPI_BF16, 128>(map_x, map_w, (bf16*)out, ldo, M, N, K, 0, status, n_sms, stream);
+    SI_TC_CASE(256);
+    SI_TC_CASE(240);
+    SI_TC_CASE(224);
+    SI_TC_CASE(208);
+    SI_TC_CASE(192);
+    SI_TC_CASE(176);
+    SI_TC_CASE(160);
+    SI_TC_CASE(144);
+    default:
+      return launch_tc<TC_EPI_BF16, 128>(map_x, map_w, (bf16*)out, ldo, M, N, K, 0, status, n_sms,
+                                         stream);
   }
+#undef SI_TC_CASE
 }
