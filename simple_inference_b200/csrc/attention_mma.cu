@@ -87,32 +87,52 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // Keys [key0, key0+64) of one sequence and one kv head into sK, sV.  Keys
 // outside [k_lo, k_hi] are zero-filled and their pages are not touched (a page
 // before the window may already belong to someone else).
-template <int ROWS>
-__device__ __forceinline__ void load_kv_tile(bf16* sK, bf16* sV, const bf16* __restrict__ pool,
-                                             const int* __restrict__ table, int key0, int k_lo,
-                                             int k_hi, int kvh, int n_kv_heads, int page_size) {
-  // Consecutive threads copy consecutive 16-byte chunks of a row, so a warp's
-  // request covers whole rows (full sectors), not half a sector per thread.
+// Where the pages of one (sequence, kv head) lie: everything the loader needs that does
+// not change from tile to tile, so that a 16-byte copy costs a handful of instructions.
+struct PageWalk {
+  const bf16* base;        // pool + kvh * page_size * D
+  const int* table;        // block table row of the sequence
+  long long page_stride;   // elements between pages: 2 * n_kv_heads * page_size * D
+  long long v_offset;      // from a key row to its value row: n_kv_heads * page_size * D
+  int page_size;
+  int page_shift;          // log2(page_size) if it is a power of two, else -1
+};
+
+__device__ __forceinline__ PageWalk make_page_walk(const bf16* pool, const int* table, int kvh,
+                                                   int n_kv_heads, int page_size) {
+  PageWalk w;
   const long long head_stride = (long long)page_size * D;
+  w.base = pool + (long long)kvh * head_stride;
+  w.table = table;
+  w.page_stride = 2LL * n_kv_heads * head_stride;
+  w.v_offset = (long long)n_kv_heads * head_stride;
+  w.page_size = page_size;
+  w.page_shift = (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;
+  return w;
+}
+
+template <int ROWS>
+__device__ __forceinline__ void load_kv_tile(bf16* sK, bf16* sV, const PageWalk& w, int key0,
+                                             int k_lo, int k_hi) {
+  // Consecutive threads copy consecutive 16-byte chunks of a row, so a warp's
+  // request covers whole rows (full sectors).  A thread keeps its chunk column
+  // and walks down the rows when the thread count is a multiple of the row's chunks.
+  constexpr int TOTAL = ROWS * CHUNKS;
 #pragma unroll
-  for (int i = 0; i < (ROWS * CHUNKS + THREADS - 1) / THREADS; ++i) {
+  for (int i = 0; i < (TOTAL + THREADS - 1) / THREADS; ++i) {
     const int idx = threadIdx.x + i * THREADS;
-    if ((ROWS * CHUNKS) % THREADS != 0 && idx >= ROWS * CHUNKS) break;
-    const int row = idx / CHUNKS, chunk = idx - row * CHUNKS;
+    if (TOTAL % THREADS != 0 && idx >= TOTAL) break;
+    const int row = idx / CHUNKS, chunk = idx - row * CHUNKS;  // CHUNKS is a constant
     const int j = key0 + row;
     const bool valid = (j >= k_lo) && (j <= k_hi);
-    const bf16* kptr = pool;
-    const bf16* vptr = pool;
+    const bf16* kptr = w.base;
     if (valid) {
-      const int lp = j / page_size;
-      const int page = table[lp];
-      const int off = j - lp * page_size;
-      kptr = pool + ((long long)page * 2 * n_kv_heads + kvh) * head_stride + (long long)off * D +
-             chunk * 8;
-      vptr = kptr + (long long)n_kv_heads * head_stride;
+      const int lp = w.page_shift >= 0 ? (j >> w.page_shift) : (j / w.page_size);
+      const int off = j - lp * w.page_size;
+      kptr = w.base + (long long)w.table[lp] * w.page_stride + (off * D + chunk * 8);
     }
     cp_async16(sK + row * STRIDE + chunk * 8, kptr, valid);
-    cp_async16(sV + row * STRIDE + chunk * 8, vptr, valid);
+    cp_async16(sV + row * STRIDE + chunk * 8, kptr + w.v_offset, valid);
   }
 }
 
@@ -244,7 +264,8 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
   const int pos0 = positions[tok0];  // rows of a tile are consecutive positions
   const int k_hi = pos0 + n_rows - 1;
   const int k_lo = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
-  const int* table = block_table + (long long)seq * table_stride;
+  const PageWalk walk = make_page_walk(pool, block_table + (long long)seq * table_stride, kvh,
+                                       n_kv_heads, page_size);
 
   const int tile_first = k_lo / PF_TILE, tile_last = k_hi / PF_TILE;
   // prologue: Q and the first PF_STAGES-1 key tiles, one commit group per tile
@@ -253,8 +274,8 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
   for (int st = 0; st < PF_STAGES - 1; ++st) {
     if (tile_first + st <= tile_last) {
       bf16* dK = sKV + st * STAGE_ELEMS;
-      load_kv_tile<PF_TILE>(dK, dK + PF_TILE * STRIDE, pool, table, (tile_first + st) * PF_TILE,
-                            k_lo, k_hi, kvh, n_kv_heads, page_size);
+      load_kv_tile<PF_TILE>(dK, dK + PF_TILE * STRIDE, walk, (tile_first + st) * PF_TILE, k_lo,
+                            k_hi);
     }
     cp_async_commit();
   }
@@ -275,8 +296,7 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
       const int nt = tile + PF_STAGES - 1;
       if (nt <= tile_last) {
         bf16* dK = sKV + ((it + PF_STAGES - 1) % PF_STAGES) * STAGE_ELEMS;
-        load_kv_tile<PF_TILE>(dK, dK + PF_TILE * STRIDE, pool, table, nt * PF_TILE, k_lo, k_hi,
-                              kvh, n_kv_heads, page_size);
+        load_kv_tile<PF_TILE>(dK, dK + PF_TILE * STRIDE, walk, nt * PF_TILE, k_lo, k_hi);
       }
       cp_async_commit();
     }
@@ -353,7 +373,8 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
   const int tok = cu_q[seq];
   const int pos = positions[tok];
   const int k_lo_all = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
-  const int* table = block_table + (long long)seq * table_stride;
+  const PageWalk walk = make_page_walk(pool, block_table + (long long)seq * table_stride, kvh,
+                                       n_kv_heads, page_size);
 
   // this block's share of the key tiles [tile_a, tile_b)
   const int tile_first = k_lo_all / KV_TILE, tile_end = pos / KV_TILE + 1;
@@ -373,8 +394,7 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
   if (tile_a < tile_b) {
     // Q rows: one per query head of the chunk, the rest zero
     load_q_rows(sQ, q + (long long)tok * q_stride + (long long)head0 * D, D, n_heads_here, 16);
-    load_kv_tile<KV_TILE>(sKV, sKV + KV_TILE * STRIDE, pool, table, tile_a * KV_TILE, k_lo_all, pos, kvh,
-                 n_kv_heads, page_size);
+    load_kv_tile<KV_TILE>(sKV, sKV + KV_TILE * STRIDE, walk, tile_a * KV_TILE, k_lo_all, pos);
     cp_async_commit();
     for (int tile = tile_a; tile < tile_b; ++tile) {
       const int stage = (tile - tile_a) & 1;
@@ -382,8 +402,7 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
       bf16* sV = sK + KV_TILE * STRIDE;
       if (tile + 1 < tile_b) {
         bf16* nK = sKV + (stage ^ 1) * 2 * KV_TILE * STRIDE;
-        load_kv_tile<KV_TILE>(nK, nK + KV_TILE * STRIDE, pool, table, (tile + 1) * KV_TILE, k_lo_all, pos,
-                     kvh, n_kv_heads, page_size);
+        load_kv_tile<KV_TILE>(nK, nK + KV_TILE * STRIDE, walk, (tile + 1) * KV_TILE, k_lo_all, pos);
         cp_async_commit();
         cp_async_wait<1>();
       } else {
