@@ -75,6 +75,7 @@ attn_generic_kernel(const T* __restrict__ q, int q_stride, const T* __restrict__
   float* ps = qs + head_dim;              // [ATT_THREADS]
   long long* voff = reinterpret_cast<long long*>(ps + ATT_THREADS);  // [ATT_THREADS]
   __shared__ float red[32];
+  pdl_wait();
 
   const int t = blockIdx.x, h = blockIdx.y;
   const int tid = threadIdx.x;
@@ -130,6 +131,7 @@ attn_generic_kernel(const T* __restrict__ q, int q_stride, const T* __restrict__
     }
     __syncthreads();  // ps / voff are rewritten by the next tile
   }
+  pdl_trigger();
   T* orow = out + (size_t)t * out_stride + (size_t)h * head_dim;
   const float inv_l = 1.0f / l_run;
   if (tid < head_dim) orow[tid] = from_f32<T>(acc0 * inv_l);

@@ -251,6 +251,7 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
   constexpr int STAGE_ELEMS = 2 * PF_TILE * STRIDE;
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  pdl_wait();
   for (int which = 0; which < 2; ++which) {
   const int tile_id = tile_pairs[2 * blockIdx.x + which];
   if (tile_id < 0) break;
@@ -343,6 +344,7 @@ attn_prefill_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __rest
   }
   cp_async_wait<0>();  // only empty groups can be pending here
   }  // which
+  pdl_trigger();
 }
 
 // -------------------------------------------------------------------- decode
@@ -363,6 +365,7 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
   bf16* sKV = sQ + 16 * STRIDE;                          // 2 stages x (K, V) x [KV_TILE][STRIDE]
 
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  pdl_wait();
   const int group = n_q_heads / n_kv_heads;
   const int chunks_per_kv = (group + 15) / 16;
   const int kvh = blockIdx.y / chunks_per_kv;
@@ -428,6 +431,7 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
     }
   }
 
+  pdl_trigger();
   // ---- merge the four warps (each saw different keys) in shared memory
   // layout: wm[4][16], wl[4][16], wacc[4][16][D] floats, over the K/V stages
   float* wm = reinterpret_cast<float*>(sKV);
@@ -485,6 +489,8 @@ __global__ void attn_merge_kernel(const float* __restrict__ part_acc,
                                   const int* __restrict__ cu_q,
                                   const int* __restrict__ single_seqs, bf16* __restrict__ out,
                                   int out_stride, int n_q_heads, int n_splits) {
+  pdl_wait();
+  pdl_trigger();
   const int head = blockIdx.y;
   const int tok = cu_q[single_seqs[blockIdx.x]];
   const long long base = ((long long)blockIdx.x * n_q_heads + head) * n_splits;

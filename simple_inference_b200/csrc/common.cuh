@@ -11,6 +11,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #define SI_API extern "C" __attribute__((visibility("default")))
 
@@ -33,6 +34,23 @@ enum SiDtype { SI_F32 = 0, SI_BF16 = 1 };
 
 namespace si {
 
+// ---------------------------------------------------------------------------
+// Programmatic dependent launch.  Kernels are launched with the "programmatic
+// stream serialization" attribute.  pdl_wait() blocks until every earlier
+// kernel of the stream has finished and its writes are visible: a kernel calls
+// it before it reads or writes anything another kernel touches (weights are
+// never written, so a product may request its first weights before waiting).
+// pdl_trigger() lets the next kernel of the stream be scheduled once all blocks
+// of this one have passed it; kernels call it when their main loop is done, so
+// that the successor's launch and prologue overlap this kernel's tail, and no
+// more than one successor is ever parked on the SMs.  A captured CUDA graph
+// keeps these edges.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void pdl_trigger() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 // Launch helper: returns the launch error instead of leaving it for later.
 template <typename Kernel, typename... Args>
 static inline cudaError_t launch(Kernel kernel, dim3 grid, dim3 block, size_t smem,
@@ -42,6 +60,12 @@ static inline cudaError_t launch(Kernel kernel, dim3 grid, dim3 block, size_t sm
   cfg.blockDim = block;
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  static const bool serial = getenv("SI_B200_NO_PDL") != nullptr;  // plain stream order, for A/B timing
+  cfg.numAttrs = serial ? 0 : 1;
   return cudaLaunchKernelEx(&cfg, kernel, args...);
 }
 

@@ -21,6 +21,7 @@ gemm_fp32_tn_kernel(const float* __restrict__ A, const float* __restrict__ W,
                     float* __restrict__ C, int M, int N, int K, int lda, int ldw, int ldc) {
   __shared__ float sA[BK][BM + 4];
   __shared__ float sW[BK][BN + 4];
+  pdl_wait();
   const int tid = threadIdx.x;
   const int tx = tid & 15, ty = tid >> 4;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
@@ -58,6 +59,7 @@ gemm_fp32_tn_kernel(const float* __restrict__ A, const float* __restrict__ W,
     }
     __syncthreads();
   }
+  pdl_trigger();
 #pragma unroll
   for (int i = 0; i < TM; ++i) {
     const int m = m0 + ty * TM + i;

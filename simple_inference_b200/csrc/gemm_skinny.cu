@@ -138,12 +138,16 @@ skinny_gemm_kernel(const bf16* __restrict__ X, int ldx, const bf16* __restrict__
   if (MT == 2) {
     // two weight tiles per warp: the second buffer would cost a resident block per SM,
     // which measures slower than the latency it hides
-    for (int batch = 0; batch < n_batches; ++batch) {
+    load_a(a0, 0);
+    pdl_wait();
+    multiply(a0, 0);
+    for (int batch = 1; batch < n_batches; ++batch) {
       load_a(a0, batch);
       multiply(a0, batch);
     }
   } else {
-    load_a(a0, 0);
+    load_a(a0, 0);  // weights are never written: request the first ones before waiting
+    pdl_wait();
     for (int batch = 0; batch < n_batches; batch += 2) {
       load_a(a1, batch + 1);   // steps past the end load nothing
       multiply(a0, batch);
@@ -152,6 +156,7 @@ skinny_gemm_kernel(const bf16* __restrict__ X, int ldx, const bf16* __restrict__
     }
   }
 
+  pdl_trigger();
   // partial sums of this warp: rows g, g+8 of each tile, tokens 2t, 2t+1 of each n-tile
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt)

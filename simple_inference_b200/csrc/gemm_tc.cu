@@ -198,6 +198,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   __syncthreads();
   tmem_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
+  pdl_wait();  // barriers and tensor memory are set up; now the inputs must be complete
 
   if (warp == 0) {
     if (lane == 0) {  // ---------------------------------------------- TMA producer
@@ -244,6 +245,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         }
         if (ok) umma_commit(acc_full0 + 8 * buf);
       }
+      pdl_trigger();  // this block has issued all its products
     }
   } else {  // ------------------------------------------------------------ epilogue
     const int quarter = warp & 3;  // a warp may read lanes [32*(warp%4), +32) of tensor memory

@@ -26,6 +26,8 @@ __global__ void rope_kv_store_kernel(T* __restrict__ qkv, const int* __restrict_
                                      int n_q_heads, int n_kv_heads, int head_dim, int page_size,
                                      int write_kv) {
   extern __shared__ float cs[];  // cos[half], sin[half]
+  pdl_wait();
+  pdl_trigger();
   const int t = blockIdx.x;
   const int half = head_dim >> 1;
   float* s_cos = cs;

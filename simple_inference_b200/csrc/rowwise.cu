@@ -15,6 +15,8 @@ namespace si {
 template <typename T>
 __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                                     float* __restrict__ out, int hidden, int vocab) {
+  pdl_wait();
+  pdl_trigger();
   const int t = blockIdx.x;
   const int id = ids[t];
   float* dst = out + (size_t)t * hidden;
@@ -39,6 +41,8 @@ __global__ void rmsnorm_kernel(float* __restrict__ residual, const TA* __restric
                                TA* __restrict__ out, int hidden, float eps) {
   extern __shared__ float srow[];
   __shared__ float red[32];
+  pdl_wait();
+  pdl_trigger();  // a short kernel: let the product that follows fetch its weights meanwhile
   const int r = blockIdx.x;
   const int src = rows ? rows[r] : r;
   float* res = residual + (size_t)src * hidden;
@@ -95,6 +99,8 @@ template <typename T, bool VEC>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, long long total,
                               int inter) {
   constexpr int W = VEC ? 8 : 1;  // inter is a multiple of 8 when VEC
+  pdl_wait();
+  pdl_trigger();
   for (long long idx = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * W; idx < total;
        idx += (long long)gridDim.x * blockDim.x * W) {
     const long long row = idx / inter;

@@ -89,6 +89,8 @@ sample_kernel(const float* __restrict__ logits, int vocab, int ld,
               int* __restrict__ out) {
   __shared__ float sv[32];
   __shared__ int sidx[32];
+  pdl_wait();
+  pdl_trigger();
   const int r = blockIdx.x;
   const float* row = logits + (size_t)r * ld;
   const float temp = temperature[r];
