@@ -1,7 +1,7 @@
 // Tensor-core attention over the paged cache for bfloat16, compiled for one
 // head size (-DSI_HEAD_DIM=D, D a multiple of 16 up to 256).
 //
-// Two kernels share one tile loader and one softmax recurrence:
+// Three kernels share one softmax recurrence:
 //
 //   attn_prefill_kernel  one block per (64-query tile of a sequence, query head):
 //                        the flash-attention forward of the reference
@@ -16,6 +16,10 @@
 //                        decode, kernels/attention_kernel.py:496-586, has one
 //                        program per query head and no split).  Partial results
 //                        go to scratch memory and attn_merge_kernel joins them.
+//   attn_decode_tma_kernel  the same, for head sizes that are multiples of 64 and pages
+//                        of 8 to 64 tokens: keys and values arrive as TMA boxes
+//                        (cp.async.bulk.tensor, 128-byte swizzle) announced by
+//                        mbarriers, and no thread computes an address.
 //
 // Both compute S = (Q K^T) * scale with mma.sync m16n8k16 (bf16 in, float32
 // accumulate), mask by absolute position (key j visible to a query at position
@@ -29,7 +33,7 @@
 // Shared-memory rows are padded by 16 bytes: the row stride is then an odd
 // multiple of 16 bytes modulo 128, which makes every ldmatrix conflict-free for
 // any D that is a multiple of 16.
-#include "common.cuh"
+#include "tma.cuh"
 
 #ifndef SI_HEAD_DIM
 #error "compile with -DSI_HEAD_DIM=<head size>"
@@ -483,6 +487,264 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
   }
 }
 
+// ------------------------------------------------------- decode, keys by TMA
+// The same kernel with keys and values brought in by the tensor memory accelerator
+// (head sizes that are multiples of 64, page sizes 8, 16, 32 or 64).  The pool of one layer
+// is a 2-D tensor [pages*2*kv_heads*page_size rows, D columns]; the keys (or values) of
+// one page and kv head are page_size consecutive rows, so one lane issues, per page and
+// 64-column half, one cp.async.bulk.tensor box with the 128-byte swizzle, and an mbarrier
+// with the expected byte count tells the four warps when a 64-key stage is complete.  The
+// warps hand a stage back through a second mbarrier, so there is no block-wide barrier in
+// the loop and nobody spends instructions on addresses.  ldmatrix applies the swizzle
+// (16-byte chunk c of row r lives at chunk c ^ (r & 7) of its 128-byte row).
+constexpr int TMA_STAGES = 2;  // measured: a third stage costs a resident block per SM and 25 % of the bandwidth
+constexpr int HALVES = D / 64;                                   // 64-column halves of a row
+constexpr int HALF_BYTES = KV_TILE * 128;                        // 64 rows x 128 B
+constexpr int TMA_STAGE_BYTES = 2 * (D >= 64 ? HALVES : 1) * HALF_BYTES;
+
+__device__ __forceinline__ const bf16* sw_addr(const bf16* half_base, int row, int chunk) {
+  return half_base + row * 64 + ((chunk ^ (row & 7)) << 3);
+}
+
+// S = Q K^T for one warp's 16 keys (rows row0..row0+15 of the stage's key halves).
+__device__ __forceinline__ void qk_tile_sw(float (&s)[2][4], const bf16* sQ, const bf16* sKhalves,
+                                           int row0) {
+  const int lane = threadIdx.x & 31;
+#pragma unroll
+  for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) s[nt][e] = 0.0f;
+#pragma unroll
+  for (int ks = 0; ks < D / 16; ++ks) {
+    uint32_t a[4], b[4];
+    ldsm_x4(a, sQ + ((lane & 7) + 8 * ((lane >> 3) & 1)) * STRIDE + ks * 16 + 8 * (lane >> 4));
+    const int row = row0 + (lane & 7) + 8 * (lane >> 4);
+    const int chunk = (ks & 3) * 2 + ((lane >> 3) & 1);
+    ldsm_x4(b, sw_addr(sKhalves + (ks >> 2) * (HALF_BYTES / 2), row, chunk));
+    mma_bf16(s[0], a, b[0], b[1]);
+    mma_bf16(s[1], a, b[2], b[3]);
+  }
+}
+
+// o += P V for one warp's 16 keys.
+__device__ __forceinline__ void pv_tile_sw(float (&o)[D / 8][4], const float (&s)[2][4],
+                                           const bf16* sVhalves, int row0) {
+  const int lane = threadIdx.x & 31;
+  uint32_t a[4];
+  a[0] = pack_bf16(s[0][0], s[0][1]);
+  a[1] = pack_bf16(s[0][2], s[0][3]);
+  a[2] = pack_bf16(s[1][0], s[1][1]);
+  a[3] = pack_bf16(s[1][2], s[1][3]);
+  const int row = row0 + (lane & 7) + 8 * ((lane >> 3) & 1);
+#pragma unroll
+  for (int dp = 0; dp < D / 16; ++dp) {
+    uint32_t b[4];
+    const int chunk = (dp & 3) * 2 + (lane >> 4);
+    ldsm_x4_trans(b, sw_addr(sVhalves + (dp >> 2) * (HALF_BYTES / 2), row, chunk));
+    mma_bf16(o[2 * dp], a, b[0], b[1]);
+    mma_bf16(o[2 * dp + 1], a, b[2], b[3]);
+  }
+}
+
+__global__ void __launch_bounds__(THREADS)
+attn_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, const bf16* __restrict__ q,
+                       int q_stride, const int* __restrict__ block_table, int table_stride,
+                       const int* __restrict__ cu_q, const int* __restrict__ positions,
+                       const int* __restrict__ single_seqs, bf16* __restrict__ out, int out_stride,
+                       float* __restrict__ part_acc, float* __restrict__ part_ml, int n_q_heads,
+                       int n_kv_heads, int page_size, float scale_log2, int window, int n_splits) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  // [stages, 1024-byte aligned][Q tile][barriers]
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t stages0 = (raw + 1023u) & ~1023u;
+  unsigned char* stages_ptr = smem_raw + (stages0 - raw);
+  bf16* sQ = reinterpret_cast<bf16*>(stages_ptr + TMA_STAGES * TMA_STAGE_BYTES);
+  const uint32_t bars = stages0 + TMA_STAGES * TMA_STAGE_BYTES + 16 * STRIDE * 2;  // 8-byte aligned
+  const uint32_t full0 = bars, empty0 = bars + 8 * TMA_STAGES;
+  __shared__ int failed;
+
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int group = n_q_heads / n_kv_heads;
+  const int chunks_per_kv = (group + 15) / 16;
+  const int kvh = blockIdx.y / chunks_per_kv;
+  const int head0 = kvh * group + (blockIdx.y % chunks_per_kv) * 16;
+  int n_heads_here = kvh * group + group - head0;
+  if (n_heads_here > 16) n_heads_here = 16;
+
+  // set-up that needs nothing from earlier kernels: barriers, zeroed stages (rows of pages
+  // that are not loaded must hold finite numbers: they meet P = 0)
+  if (tid == 0) {
+    failed = 0;
+    for (int st = 0; st < TMA_STAGES; ++st) {
+      mbar_init(full0 + 8 * st, 1);
+      mbar_init(empty0 + 8 * st, 4);  // one arrival per warp
+    }
+    mbar_init_fence();
+  }
+  pdl_wait();
+  const int seq = single_seqs[blockIdx.x];
+  const int tok = cu_q[seq];
+  const int pos = positions[tok];
+  const int k_lo_all = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  const int* table = block_table + (long long)seq * table_stride;
+
+  const int tile_first = k_lo_all / KV_TILE, tile_end = pos / KV_TILE + 1;
+  const int n_tiles_all = tile_end - tile_first;
+  const int per = (n_tiles_all + n_splits - 1) / n_splits;
+  const int tile_a = tile_first + blockIdx.z * per;
+  int tile_b = tile_a + per;
+  if (tile_b > tile_end) tile_b = tile_end;
+  const int n_my = tile_b - tile_a;
+
+  // Rows of pages that are not loaded (past the last key, or before the window) must hold
+  // finite numbers, since they meet P = 0.  A stage that a complete tile filled before is
+  // fine; only a stage whose FIRST tile is such a partial one is cleared here.
+  for (int st = 0; st < TMA_STAGES && st < n_my; ++st) {
+    const int t = tile_a + st;
+    const bool partial = (t == tile_end - 1 && (pos + 1) % KV_TILE != 0) ||
+                         (t == tile_first && k_lo_all % KV_TILE != 0);
+    if (partial) {
+      uint4* z = reinterpret_cast<uint4*>(stages_ptr + st * TMA_STAGE_BYTES);
+      for (int i = tid; i < TMA_STAGE_BYTES / 16; i += THREADS) z[i] = make_uint4(0, 0, 0, 0);
+    }
+  }
+  fence_proxy_async_smem();
+
+  // Q rows by cp.async: one per query head of the chunk, the rest zero
+  if (n_my > 0) load_q_rows(sQ, q + (long long)tok * q_stride + (long long)head0 * D, D, n_heads_here, 16);
+  cp_async_commit();
+  cp_async_wait<0>();
+  __syncthreads();  // barriers initialised, stages zeroed, Q in place
+
+  // one lane issues the boxes of tile number `i` of this block into stage i % TMA_STAGES
+  const int pages_per_tile = KV_TILE / page_size;
+  auto issue = [&](int i) {
+    const int st = i % TMA_STAGES;
+    const int key0 = (tile_a + i) * KV_TILE;
+    const uint32_t dst0 = stages0 + st * TMA_STAGE_BYTES;
+    int n_boxes = 0;
+    for (int pg = 0; pg < pages_per_tile; ++pg) {
+      const int j0 = key0 + pg * page_size;
+      if (j0 <= pos && j0 + page_size - 1 >= k_lo_all) ++n_boxes;
+    }
+    mbar_expect_tx(full0 + 8 * st, (uint32_t)n_boxes * 2u * HALVES * page_size * 128u);
+    for (int pg = 0; pg < pages_per_tile; ++pg) {
+      const int j0 = key0 + pg * page_size;
+      if (!(j0 <= pos && j0 + page_size - 1 >= k_lo_all)) continue;
+      const int page = table[j0 / page_size];
+      const int krow = ((page * 2) * n_kv_heads + kvh) * page_size;
+      const int vrow = krow + n_kv_heads * page_size;
+#pragma unroll
+      for (int h = 0; h < HALVES; ++h) {
+        tma_load_2d(dst0 + h * HALF_BYTES + pg * page_size * 128, &pool_map, full0 + 8 * st, h * 64, krow);
+        tma_load_2d(dst0 + (HALVES + h) * HALF_BYTES + pg * page_size * 128, &pool_map,
+                    full0 + 8 * st, h * 64, vrow);
+      }
+    }
+  };
+  if (tid == 0)
+    for (int i = 0; i < TMA_STAGES - 1 && i < n_my; ++i) issue(i);
+
+  float o[D / 8][4];
+#pragma unroll
+  for (int dt = 0; dt < D / 8; ++dt)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[dt][e] = 0.0f;
+  float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.0f, 0.0f};
+
+  bool ok = true;
+  for (int i = 0; i < n_my && ok; ++i) {
+    const int st = i % TMA_STAGES;
+    const uint32_t use = (uint32_t)(i / TMA_STAGES);  // how often this stage was used before
+    if (tid == 0) {  // refill the stage that tile i-1 used, once all four warps have left it
+      const int nx = i + TMA_STAGES - 1;
+      if (nx < n_my) {
+        const int nst = nx % TMA_STAGES;
+        const uint32_t nuse = (uint32_t)(nx / TMA_STAGES);
+        if (nuse == 0 || mbar_wait_bounded(empty0 + 8 * nst, (nuse - 1) & 1u)) issue(nx);
+        else atomicExch(&failed, 1);
+      }
+    }
+    __syncwarp();
+    if (!mbar_wait_bounded(full0 + 8 * st, use & 1u)) {
+      atomicExch(&failed, 1);
+      ok = false;
+      break;
+    }
+    const bf16* sK = reinterpret_cast<const bf16*>(stages_ptr + st * TMA_STAGE_BYTES);
+    const bf16* sV = sK + HALVES * (HALF_BYTES / 2);
+    const int key0 = (tile_a + i) * KV_TILE + warp * 16;
+    if (key0 <= pos && key0 + 15 >= k_lo_all) {
+      float s[2][4];
+      qk_tile_sw(s, sQ, sK, warp * 16);
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int j = key0 + nt * 8 + (lane & 3) * 2 + (e & 1);
+          const bool in = j <= pos && j >= k_lo_all;
+          s[nt][e] = in ? s[nt][e] * scale_log2 : -INFINITY;
+        }
+      softmax_update<2>(s, m, l, o);
+      pv_tile_sw(o, s, sV, warp * 16);
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(empty0 + 8 * st);
+  }
+  __syncthreads();  // every warp has left the stages: the space is reused for the merge
+  pdl_trigger();
+  const bool bad = failed != 0;
+
+  float* wm = reinterpret_cast<float*>(stages_ptr);
+  float* wl = wm + 4 * 16;
+  float* wacc = wl + 4 * 16;
+#pragma unroll
+  for (int r = 0; r < 2; ++r) {
+    float lt = l[r];
+    lt += __shfl_xor_sync(0xffffffffu, lt, 1);
+    lt += __shfl_xor_sync(0xffffffffu, lt, 2);
+    const int row = (lane >> 2) + 8 * r;
+    if ((lane & 3) == 0) {
+      wm[warp * 16 + row] = m[r];
+      wl[warp * 16 + row] = lt;
+    }
+#pragma unroll
+    for (int dt = 0; dt < D / 8; ++dt) {
+      float* dst = wacc + ((warp * 16 + row) * D) + dt * 8 + (lane & 3) * 2;
+      dst[0] = o[dt][2 * r];
+      dst[1] = o[dt][2 * r + 1];
+    }
+  }
+  __syncthreads();
+  for (int idx = tid; idx < n_heads_here * D; idx += THREADS) {
+    const int row = idx / D, d = idx - row * D;
+    float mm = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) mm = fmaxf(mm, wm[w * 16 + row]);
+    float acc = 0.0f, lsum = 0.0f;
+    if (mm != -INFINITY) {
+#pragma unroll
+      for (int w = 0; w < 4; ++w) {
+        const float f = exp2f(wm[w * 16 + row] - mm);
+        acc += f * wacc[(w * 16 + row) * D + d];
+        lsum += f * wl[w * 16 + row];
+      }
+    }
+    if (bad) acc = __int_as_float(0x7fc00000);  // a wait ran out: make the failure visible
+    const int head = head0 + row;
+    if (n_splits == 1) {
+      out[(long long)tok * out_stride + (long long)head * D + d] = from_f32<bf16>(acc / lsum);
+    } else {
+      const long long p = ((long long)blockIdx.x * n_q_heads + head) * n_splits + blockIdx.z;
+      part_acc[p * D + d] = acc;
+      if (d == 0) {
+        part_ml[p * 2] = bad ? 0.0f : mm;
+        part_ml[p * 2 + 1] = bad ? 1.0f : lsum;
+      }
+    }
+  }
+}
+
 // grid (sequences with one token, query heads); joins the splits' partial results.
 __global__ void attn_merge_kernel(const float* __restrict__ part_acc,
                                   const float* __restrict__ part_ml,
@@ -513,6 +775,8 @@ constexpr size_t PREFILL_SMEM =
     (size_t)(Q_TILE + PF_STAGES * 2 * PF_TILE) * STRIDE * sizeof(bf16);
 constexpr size_t DECODE_KV_SMEM = (size_t)4 * KV_TILE * STRIDE * sizeof(bf16);
 constexpr size_t DECODE_MERGE_SMEM = (size_t)(2 * 4 * 16 + 4 * 16 * D) * sizeof(float);
+constexpr size_t DECODE_TMA_SMEM =
+    1024 + (size_t)TMA_STAGES * TMA_STAGE_BYTES + 16 * STRIDE * sizeof(bf16) + 16 * TMA_STAGES + 64;
 constexpr size_t DECODE_SMEM =
     (size_t)16 * STRIDE * sizeof(bf16) +
     (DECODE_KV_SMEM > DECODE_MERGE_SMEM ? DECODE_KV_SMEM : DECODE_MERGE_SMEM);
@@ -561,11 +825,13 @@ SI_API long long si_attn_decode_scratch_floats(int n_single, int n_q_heads, int 
 
 // Attention for the sequences listed in single_seqs (one token each).
 // scratch: si_attn_decode_scratch_floats(...) floats, may be null when n_splits == 1.
-SI_API int si_attn_decode(const void* q, int q_stride, const void* pool, const int* block_table,
-                          int table_stride, const int* cu_q, const int* positions,
-                          const int* single_seqs, int n_single, void* out, int out_stride,
-                          float* scratch, int n_q_heads, int n_kv_heads, int page_size,
-                          float scale, int window, int n_splits, cudaStream_t stream) {
+// n_pages: pages in the pool (for the bounds of the tensor map).
+SI_API int si_attn_decode(const void* q, int q_stride, const void* pool, int n_pages,
+                          const int* block_table, int table_stride, const int* cu_q,
+                          const int* positions, const int* single_seqs, int n_single, void* out,
+                          int out_stride, float* scratch, int n_q_heads, int n_kv_heads,
+                          int page_size, float scale, int window, int n_splits,
+                          cudaStream_t stream) {
   if (!q || !pool || !block_table || !cu_q || !positions || !single_seqs || !out)
     return SI_ERR_ARG;
   if (n_single < 0 || n_q_heads <= 0 || n_kv_heads <= 0 || n_q_heads % n_kv_heads != 0 ||
@@ -587,6 +853,33 @@ SI_API int si_attn_decode(const void* q, int q_stride, const void* pool, const i
   float* part_acc = scratch;
   float* part_ml = scratch ? scratch + (long long)n_single * n_q_heads * n_splits * si::D : nullptr;
   dim3 grid(n_single, grid_y, n_splits);
+  // keys by TMA when the shapes allow it (see attn_decode_tma_kernel)
+  const bool tma_shapes = si::D % 64 == 0 && page_size >= 8 && page_size <= 64 &&
+                          (page_size & (page_size - 1)) == 0 && n_pages > 0 &&
+                          (((uintptr_t)pool) & 15) == 0;
+  CUtensorMap pool_map;
+  if (tma_shapes &&
+      si::make_bf16_map(&pool_map, pool, (long long)n_pages * 2 * n_kv_heads * page_size, si::D,
+                        si::D, page_size)) {
+    static bool tma_configured = false;
+    if (!tma_configured) {
+      cudaError_t e = cudaFuncSetAttribute(si::attn_decode_tma_kernel,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           (int)si::DECODE_TMA_SMEM);
+      if (e != cudaSuccess) return (int)e;
+      tma_configured = true;
+    }
+    SI_LAUNCH(si::attn_decode_tma_kernel, grid, si::THREADS, si::DECODE_TMA_SMEM, stream, pool_map,
+              (const si::bf16*)q, q_stride, block_table, table_stride, cu_q, positions, single_seqs,
+              (si::bf16*)out, out_stride, part_acc, part_ml, n_q_heads, n_kv_heads, page_size,
+              scale * si::LOG2E, window, n_splits);
+    if (n_splits > 1) {
+      dim3 mgrid(n_single, n_q_heads);
+      SI_LAUNCH(si::attn_merge_kernel, mgrid, si::D >= 128 ? 128 : 64, 0, stream, part_acc, part_ml,
+                cu_q, single_seqs, (si::bf16*)out, out_stride, n_q_heads, n_splits);
+    }
+    return SI_OK;
+  }
   SI_LAUNCH(si::attn_decode_kernel, grid, si::THREADS, si::DECODE_SMEM, stream,
       (const si::bf16*)q, q_stride, (const si::bf16*)pool, block_table, table_stride, cu_q,
       positions, single_seqs, (si::bf16*)out, out_stride, part_acc, part_ml, n_q_heads, n_kv_heads,
@@ -613,7 +906,7 @@ constexpr int kMaxDevices = 64;
 float* g_static_scratch[kMaxDevices];  // device address of si_static_scratch, per device
 }  // namespace
 
-SI_API int si_attn_decode_static(const void* q, int q_stride, const void* pool,
+SI_API int si_attn_decode_static(const void* q, int q_stride, const void* pool, int n_pages,
                                  const int* block_table, int table_stride, const int* cu_q,
                                  const int* positions, const int* single_seqs, int n_single,
                                  void* out, int out_stride, int n_q_heads, int n_kv_heads,
@@ -633,7 +926,7 @@ SI_API int si_attn_decode_static(const void* q, int q_stride, const void* pool,
     if (ptr == nullptr) return SI_ERR_ARG;
     g_static_scratch[dev] = ptr;
   }
-  return si_attn_decode(q, q_stride, pool, block_table, table_stride, cu_q, positions, single_seqs,
+  return si_attn_decode(q, q_stride, pool, n_pages, block_table, table_stride, cu_q, positions, single_seqs,
                         n_single, out, out_stride, g_static_scratch[dev], n_q_heads, n_kv_heads,
                         page_size, scale, window, n_splits, stream);
 }

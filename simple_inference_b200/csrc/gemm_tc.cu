@@ -29,13 +29,7 @@
 // Every wait on an mbarrier is bounded.  If one runs out, the block records a
 // code in *status, stops issuing work, still meets its final barrier, frees its
 // tensor memory and returns; the host reads *status and raises.
-#include <cuda.h>
-
-#include <functional>
-#include <mutex>
-#include <unordered_map>
-
-#include "common.cuh"
+#include "tma.cuh"
 
 namespace si {
 
@@ -48,52 +42,16 @@ constexpr uint32_t TC_B_BYTES = TC_BN_MAX * TC_BK * 2;   // 32 KiB reserved; a n
 constexpr uint32_t TC_STAGE_BYTES = TC_A_BYTES + TC_B_BYTES;
 constexpr uint32_t TC_TMEM_COLS = 512;                   // two accumulators of up to 256 columns
 constexpr uint32_t TC_SMEM_BYTES = TC_STAGES * TC_STAGE_BYTES + 1024 /*alignment*/ + 256 /*barriers*/;
-constexpr unsigned long long TC_WAIT_LIMIT_NS = 1000000000ull;  // one second per wait
 
 enum TcStatus { TC_OK = 0, TC_TIMEOUT_PRODUCER = 1, TC_TIMEOUT_MMA = 2, TC_TIMEOUT_EPILOGUE = 3 };
 enum TcEpilogue { TC_EPI_BF16 = 0, TC_EPI_SWIGLU = 2 };
 
 // ------------------------------------------------------------------ PTX helpers
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return (uint32_t)__cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-// Bounded wait for the phase with the given parity.  False (and *status set) on time-out.
-__device__ __forceinline__ unsigned long long global_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
+// (mbarrier and TMA helpers are in tma.cuh)
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* status, int code) {
-  const unsigned long long t0 = global_ns();
-  for (uint32_t spin = 0;; ++spin) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done) : "r"(bar), "r"(parity) : "memory");
-    if (done) return true;
-    if ((spin & 63u) == 63u && global_ns() - t0 > TC_WAIT_LIMIT_NS) break;
-  }
+  if (mbar_wait_bounded(bar, parity)) return true;
   atomicCAS(status, 0, code);
   return false;
-}
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
-                                            int x, int y) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
-      " [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
 }
 // Shared-memory operand descriptor: K-major rows of 128 bytes, 128-byte swizzle, groups of
 // 8 rows 1024 bytes apart (what a TMA box of 64 bfloat16 columns with SWIZZLE_128B writes).
@@ -187,7 +145,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
       mbar_init(acc_full0 + 8 * b, 1);
       mbar_init(acc_empty0 + 8 * b, 4);  // one arrival per epilogue warp
     }
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    mbar_init_fence();
   }
   if (warp == 1) {  // the whole warp allocates tensor memory, and later frees it
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
@@ -340,64 +298,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
 }
 
 // ------------------------------------------------------------------------- host
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
-                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_tiled_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (!fn) {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(p);
-  }
-  return fn;
-}
-
-// rows x cols bfloat16 matrix with `ld` elements between rows; boxes of box_rows x 64 columns.
-// Encoding a map costs tens of microseconds of host time, and a step asks for the same few
-// (pointer, shape) combinations again and again, so the encoded maps are kept.
-struct MapKey {
-  const void* ptr;
-  int rows, cols, ld, box_rows;
-  bool operator==(const MapKey& o) const {
-    return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
-  }
-};
-struct MapKeyHash {
-  size_t operator()(const MapKey& k) const {
-    size_t h = std::hash<const void*>()(k.ptr);
-    for (int v : {k.rows, k.cols, k.ld, k.box_rows}) h = h * 1000003u + (size_t)v;
-    return h;
-  }
-};
-static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> g_maps;
-static std::mutex g_maps_mutex;
-
 static bool make_map(CUtensorMap* map, const void* ptr, int rows, int cols, int ld, int box_rows) {
-  const MapKey key{ptr, rows, cols, ld, box_rows};
-  std::lock_guard<std::mutex> lock(g_maps_mutex);
-  auto it = g_maps.find(key);
-  if (it != g_maps.end()) {
-    *map = it->second;
-    return true;
-  }
-  EncodeTiledFn fn = encode_tiled_fn();
-  if (!fn) return false;
-  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * sizeof(bf16)};
-  cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows};
-  cuuint32_t elem[2] = {1, 1};
-  if (fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
-         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-    return false;
-  if (g_maps.size() > 4096) g_maps.clear();
-  g_maps.emplace(key, *map);
-  return true;
+  return make_bf16_map(map, ptr, rows, cols, ld, box_rows);
 }
 
 // Tile width for an [M, N] output on n_sms persistent blocks: the widest tile is the most

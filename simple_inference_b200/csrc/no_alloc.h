@@ -38,8 +38,8 @@
 extern "C" {
 #endif
 
-int si_attn_decode_static(const void* q, int q_stride, const void* pool, const int* block_table,
-                          int table_stride, const int* cu_q, const int* positions,
+int si_attn_decode_static(const void* q, int q_stride, const void* pool, int n_pages,
+                          const int* block_table, int table_stride, const int* cu_q, const int* positions,
                           const int* single_seqs, int n_single, void* out, int out_stride,
                           int n_q_heads, int n_kv_heads, int page_size, float scale, int window,
                           int n_splits, cudaStream_t stream);

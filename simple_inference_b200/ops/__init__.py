@@ -377,7 +377,7 @@ def paged_attention(q: torch.Tensor, pool: torch.Tensor, ctx, group: int, out: t
                                  (ctx.n_single, num_q_heads * MAX_KV_SPLITS * (head_dim + 2)),
                                  torch.float32, row_cap=ctx.max_seqs)
         _check(lib.si_attn_decode(
-            _p(q), q.stride(0), _p(pool), _p(table), table.stride(0), _p(ctx.cu_q),
+            _p(q), q.stride(0), _p(pool), pool.shape[0], _p(table), table.stride(0), _p(ctx.cu_q),
             _p(ctx.positions), _p(ctx.single_seqs), ctx.n_single, _p(out), out.stride(0),
             _p(scratch), num_q_heads, num_kv_heads, page_size, _c_float(scale), win, n_splits,
             _stream()), "attn_decode", kernels=2 if n_splits > 1 else 1)

@@ -50,7 +50,8 @@ def _case(n_seqs, ctx_lens, hq, hkv, d, ps, seed):
 def _call(lib, fn_name, c, out, n_splits, scratch=None):
     P = lambda t: ctypes.c_void_p(t.data_ptr())  # noqa: E731
     stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
-    head = [P(c["q"]), c["q"].stride(0), P(c["pool"]), P(c["table"]), c["table"].stride(0),
+    head = [P(c["q"]), c["q"].stride(0), P(c["pool"]), c["pool"].shape[0], P(c["table"]),
+            c["table"].stride(0),
             P(c["cu_q"]), P(c["positions"]), P(c["single"]), c["n"], P(out), out.stride(0)]
     tail = [c["hq"], c["hkv"], c["ps"], ctypes.c_float(1 / math.sqrt(c["d"])), 0, n_splits, stream]
     if scratch is not None:
