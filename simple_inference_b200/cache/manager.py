@@ -115,6 +115,8 @@ class CacheManager:
         heapq.heapify(self._free_slots)
         self._slot_of: dict[Hashable, int] = {}
         self._length: dict[Hashable, int] = {}
+        self._admission: dict[Hashable, int] = {}   # request -> serial number of its admission
+        self._admissions = 0
 
     # ----------------------------------------------------------- admission
     def fits_at_all(self, total_tokens: int) -> bool:
@@ -140,6 +142,8 @@ class CacheManager:
         slot = heapq.heappop(self._free_slots)
         self._slot_of[request] = slot
         self._length[request] = 0
+        self._admissions += 1
+        self._admission[request] = self._admissions
         for t in self.state.values():
             t[slot].zero_()
         return slot
@@ -174,6 +178,7 @@ class CacheManager:
             del g.requests[request]
         heapq.heappush(self._free_slots, self._slot_of.pop(request))
         del self._length[request]
+        del self._admission[request]
 
     # -------------------------------------------------------------- growth
     def length(self, request: Hashable) -> int:
@@ -181,6 +186,10 @@ class CacheManager:
 
     def slot(self, request: Hashable) -> int:
         return self._slot_of[request]
+
+    def admission(self, request: Hashable) -> int:
+        """Serial number of this admission: tells a request from an earlier one of the same name."""
+        return self._admission[request]
 
     def is_admitted(self, request: Hashable) -> bool:
         return request in self._slot_of

@@ -166,6 +166,10 @@ class BatchBuilder:
         self.dev = torch.zeros(self.total, dtype=torch.int32, device=device)
         self._copied = torch.cuda.Event() if pin else None
         self._copy_pending = False
+        # what each block-table row of the host buffer holds: (admission serial, entries written),
+        # so that a request that keeps its row from step to step only appends its new pages
+        self._row_owner: list[list[tuple[int, int] | None]] = [
+            [None] * max_seqs for _ in range(self.n_groups)]
 
     def _h(self, name: str) -> np.ndarray:
         o, n = self._off[name]
@@ -215,18 +219,39 @@ class BatchBuilder:
             if end > self.max_seq_len:
                 raise ValueError(f"request {e.request!r} would reach {end} tokens, beyond "
                                  f"max_seq_len {self.max_seq_len}")
-            token_ids[t:t + n] = e.tokens
-            positions[t:t + n] = np.arange(start, end, dtype=np.int32)
-            tok_seq[t:t + n] = s
             seq_slots[s] = cache.slot(e.request)
+            if n == 1:
+                token_ids[t] = e.tokens[0]
+                positions[t] = start
+                tok_seq[t] = s
+            else:
+                token_ids[t:t + n] = e.tokens
+                positions[t:t + n] = np.arange(start, end, dtype=np.int32)
+                tok_seq[t:t + n] = s
             for g, grp in enumerate(cache.groups):
                 table = cache.block_table(e.request, g)
                 row = tables[g][s]
-                row[:len(table)] = table
-                pages = np.asarray(table, dtype=np.int64)[np.arange(start, end) // grp.page_size]
-                if (pages < 0).any():
-                    raise RuntimeError(f"request {e.request!r} writes to a page already given back")
-                kv_slots[g][t:t + n] = pages * grp.page_size + np.arange(start, end) % grp.page_size
+                owner = self._row_owner[g][s]
+                serial = cache.admission(e.request)
+                if grp.spec.window is None and owner is not None and owner[0] == serial \
+                        and owner[1] <= len(table):
+                    if owner[1] < len(table):
+                        row[owner[1]:len(table)] = table[owner[1]:]   # only the new pages
+                else:
+                    row[:len(table)] = table
+                self._row_owner[g][s] = (serial, len(table))
+                ps = grp.page_size
+                if n == 1:
+                    page = table[start // ps]
+                    if page < 0:
+                        raise RuntimeError(f"request {e.request!r} writes to a page already given back")
+                    kv_slots[g][t] = page * ps + start % ps
+                else:
+                    where = np.arange(start, end)
+                    pages = np.asarray(table, dtype=np.int64)[where // ps]
+                    if (pages < 0).any():
+                        raise RuntimeError(f"request {e.request!r} writes to a page already given back")
+                    kv_slots[g][t:t + n] = pages * ps + where % ps
             for w in e.want:
                 if not (0 <= w < n):
                     raise ValueError(f"want index {w} outside the {n} tokens of {e.request!r}")
@@ -250,6 +275,7 @@ class BatchBuilder:
             seq_slots[s] = cache.scratch_slot
             for g, grp in enumerate(cache.groups):
                 tables[g][s, 0] = grp.scratch_page
+                self._row_owner[g][s] = None
                 kv_slots[g][t] = grp.scratch_page * grp.page_size
             single[n_single] = s; n_single += 1
             logit_rows[r] = t; r += 1
