@@ -1,0 +1,403 @@
+// Prefill attention on the fifth-generation tensor cores (head size 128, pages of 8 to 64
+// tokens): the flash-attention forward of the reference (kernels/attention_kernel.py:108-251)
+// over the paged cache, with both matrix products as tcgen05.mma and their results in tensor
+// memory.
+//
+// One block per (128-query tile of a sequence, query head); keys in tiles of 128.  Roles:
+//   warp 0             TMA producer: the Q tile once (two 64-column halves, straight from
+//                      the qkv buffer), then per key tile the K and V rows of its pages
+//                      (cp.async.bulk.tensor boxes of page_size x 64, 128-byte swizzle; one
+//                      lane per page) into a two-stage ring; mbarriers count the bytes.
+//   warp 1, one lane   MMA issuer: S = Q K^T (M128 N128, eight K16 steps; Q and K are
+//                      K-major) into one of two S buffers in tensor memory, and
+//                      PV = P V (P is K-major in shared memory, V is MN-major: its rows are
+//                      keys) into one of two output buffers.  S of the next tile is issued
+//                      before PV of this one, so the tensor core works while softmax runs.
+//   warps 2..9         softmax, two threads per query row (64 keys and 64 output columns
+//                      each): read S with tcgen05.ld, trade the row maximum through shared
+//                      memory, mask edge tiles by absolute position, online softmax in
+//                      float32 (kernels/attention_kernel.py:231-241), round P to bfloat16
+//                      (:240) and write it to shared memory in the operand layout; read each
+//                      tile's PV from tensor memory and keep O = O*alpha + PV in registers;
+//                      at the end divide by l and store.
+// Every mbarrier wait is bounded; a block whose wait runs out writes NaN to its outputs.
+#include "tcgen05.cuh"
+
+#ifndef SI_HEAD_DIM
+#error "compile with -DSI_HEAD_DIM=<head size>"
+#endif
+
+#if SI_HEAD_DIM == 128
+
+namespace si {
+
+typedef __nv_bfloat16 bf16;
+constexpr int TQ = 128, TK = 128, HD = 128;
+constexpr uint32_t HALF_BYTES_TC = 128 * 128;        // 128 rows x 64 bf16
+constexpr uint32_t TILE_BYTES = 2 * HALF_BYTES_TC;   // 128 x 128 bf16 = 32 KiB
+constexpr int ATC_THREADS = 320;  // producer warp, MMA warp, eight softmax warps
+constexpr uint32_t ATC_SMEM = 1024 + 6 * TILE_BYTES + 256;  // Q, K0, K1, V0, V1, P + barriers
+constexpr float LOG2E_TC = 1.4426950408889634f;
+
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+__global__ void __launch_bounds__(ATC_THREADS, 1)
+attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
+                       const __grid_constant__ CUtensorMap kv_map,
+                       const int* __restrict__ block_table, int table_stride,
+                       const int* __restrict__ cu_q, const int* __restrict__ positions,
+                       const int* __restrict__ tile_seq, const int* __restrict__ tile_start,
+                       bf16* __restrict__ out, int out_stride, int n_q_heads, int n_kv_heads,
+                       int page_size, float scale_log2, int window) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw = smem_u32(smem_raw);
+  const uint32_t base = (raw + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - raw);
+  const uint32_t sQ = base, sK0 = base + TILE_BYTES, sV0 = base + 3 * TILE_BYTES,
+                 sP = base + 5 * TILE_BYTES;
+  const uint32_t bars = base + 6 * TILE_BYTES;
+  // barriers, 8 bytes each
+  const uint32_t q_full = bars, kv_full0 = bars + 8, kv_empty0 = bars + 24, s_full0 = bars + 40,
+                 s_empty0 = bars + 56, p_full = bars + 72, p_empty = bars + 80,
+                 o_full0 = bars + 88, o_empty0 = bars + 104, tmem_slot = bars + 120;
+  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(base_ptr + 6 * TILE_BYTES + 120);
+  __shared__ int failed;
+  __shared__ float xmax[2][2][TQ];  // [tile parity][part][row]: the two threads of a row trade maxima
+  __shared__ float xsum[2][TQ];
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    failed = 0;
+    mbar_init(q_full, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(kv_full0 + 8 * i, 1);
+      mbar_init(kv_empty0 + 8 * i, 1);
+      mbar_init(s_full0 + 8 * i, 1);
+      mbar_init(s_empty0 + 8 * i, 8);
+      mbar_init(o_full0 + 8 * i, 1);
+      mbar_init(o_empty0 + 8 * i, 8);
+    }
+    mbar_init(p_full, 8);
+    mbar_init(p_empty, 1);
+    mbar_init_fence();
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(tmem_slot), "r"(512u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    tmem_fence_before();
+  }
+  // K/V stages start as zeros: rows of pages that are not loaded meet P = 0 and must be finite
+  {
+    uint4* z = reinterpret_cast<uint4*>(base_ptr + TILE_BYTES);
+    for (int i = threadIdx.x; i < (int)(4 * TILE_BYTES / 16); i += ATC_THREADS)
+      z[i] = make_uint4(0, 0, 0, 0);
+  }
+  fence_proxy_async_smem();
+  __syncthreads();
+  tmem_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+  pdl_wait();
+
+  // ---- this block's tile
+  const int tile_id = blockIdx.y;  // the host lists the longest tiles first; heads vary fastest
+  const int seq = tile_seq[tile_id];
+  const int tok0 = cu_q[seq] + tile_start[tile_id];
+  int n_rows = cu_q[seq + 1] - tok0;
+  if (n_rows > TQ) n_rows = TQ;
+  const int h = blockIdx.x;
+  const int kvh = h / (n_q_heads / n_kv_heads);
+  const int pos0 = positions[tok0];
+  const int k_hi = pos0 + n_rows - 1;
+  const int k_lo = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
+  const int tile_first = k_lo / TK, tile_last = k_hi / TK;
+  const int n_tiles = tile_last - tile_first + 1;
+  const int* table = block_table + (long long)seq * table_stride;
+
+  if (warp == 0) {  // ----------------------------------------------------------- TMA producer
+    // Lane i looks up and fetches page i of a key tile, so the table reads of a tile are in
+    // flight together, and those of the next tile while this one's stage is awaited.
+    if (lane == 0) {
+      mbar_expect_tx(q_full, TILE_BYTES);
+      tma_load_2d(sQ, &q_map, q_full, h * HD, tok0);
+      tma_load_2d(sQ + HALF_BYTES_TC, &q_map, q_full, h * HD + 64, tok0);
+    }
+    const int pages_per_tile = TK / page_size;  // at most 16
+    auto page_of = [&](int t) {
+      const int j0 = (tile_first + t) * TK + lane * page_size;
+      const bool wanted = lane < pages_per_tile && j0 <= k_hi && j0 + page_size - 1 >= k_lo;
+      return wanted ? table[j0 / page_size] : -1;
+    };
+    int page_next = n_tiles > 0 ? page_of(0) : -1;
+    for (int t = 0; t < n_tiles; ++t) {
+      const int st = t & 1;
+      const int page = page_next;
+      if (t + 1 < n_tiles) page_next = page_of(t + 1);
+      bool ok = true;
+      if (t >= 2) ok = mbar_wait_bounded(kv_empty0 + 8 * st, ((t >> 1) - 1) & 1);
+      if (!__all_sync(0xffffffffu, ok)) {
+        if (lane == 0) atomicExch(&failed, 1);
+        break;
+      }
+      const int n_pages = __popc(__ballot_sync(0xffffffffu, page >= 0));
+      if (lane == 0)
+        mbar_expect_tx(kv_full0 + 8 * st, (uint32_t)n_pages * 4u * page_size * 128u);
+      __syncwarp();
+      if (page >= 0) {
+        const uint32_t dK = sK0 + st * TILE_BYTES, dV = sV0 + st * TILE_BYTES;
+        const int krow = ((page * 2) * n_kv_heads + kvh) * page_size;
+        const int vrow = krow + n_kv_heads * page_size;
+        const uint32_t off = lane * page_size * 128;
+        tma_load_2d(dK + off, &kv_map, kv_full0 + 8 * st, 0, krow);
+        tma_load_2d(dK + HALF_BYTES_TC + off, &kv_map, kv_full0 + 8 * st, 64, krow);
+        tma_load_2d(dV + off, &kv_map, kv_full0 + 8 * st, 0, vrow);
+        tma_load_2d(dV + HALF_BYTES_TC + off, &kv_map, kv_full0 + 8 * st, 64, vrow);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {  // --------------------------------------------------------- MMA issuer
+      constexpr uint32_t idesc_s = umma_idesc(TQ, TK, false);   // Q K^T: both K-major
+      constexpr uint32_t idesc_o = umma_idesc(TQ, HD, true);    // P V: V is MN-major
+      bool ok = mbar_wait_bounded(q_full, 0);
+      auto issue_s = [&](int t) {
+        const int b = t & 1;
+        if (!mbar_wait_bounded(kv_full0 + 8 * b, (t >> 1) & 1)) return false;
+        if (t >= 2 && !mbar_wait_bounded(s_empty0 + 8 * b, ((t >> 1) - 1) & 1)) return false;
+        tmem_fence_after();
+        const uint32_t kbase = sK0 + b * TILE_BYTES;
+#pragma unroll
+        for (int k = 0; k < HD / 16; ++k) {  // 16 columns of d per step; halves of 64 columns
+          const uint32_t hoff = (k >> 2) * HALF_BYTES_TC + (k & 3) * 32;
+          umma_bf16(tmem_base + b * 128, umma_desc(sQ + hoff), umma_desc(kbase + hoff), idesc_s,
+                    k != 0 ? 1u : 0u);
+        }
+        umma_commit(s_full0 + 8 * b);
+        return true;
+      };
+      auto issue_pv = [&](int t) {
+        const int b = t & 1;
+        if (!mbar_wait_bounded(p_full, t & 1)) return false;
+        if (t >= 2 && !mbar_wait_bounded(o_empty0 + 8 * b, ((t >> 1) - 1) & 1)) return false;
+        tmem_fence_after();
+        const uint32_t vbase = sV0 + b * TILE_BYTES;
+#pragma unroll
+        for (int k = 0; k < TK / 16; ++k) {  // 16 keys per step
+          const uint64_t da = umma_desc(sP + (k >> 2) * HALF_BYTES_TC + (k & 3) * 32);
+          const uint64_t db = umma_desc_mn(vbase + k * 2048, HALF_BYTES_TC);  // 16 keys = 2 groups of 8 rows
+          umma_bf16(tmem_base + 256 + b * 128, da, db, idesc_o, k != 0 ? 1u : 0u);
+        }
+        umma_commit(o_full0 + 8 * b);
+        umma_commit(kv_empty0 + 8 * b);
+        umma_commit(p_empty);
+        return true;
+      };
+      if (ok) ok = issue_s(0);
+      for (int t = 0; ok && t < n_tiles; ++t) {
+        if (t + 1 < n_tiles) ok = issue_s(t + 1);
+        if (ok) ok = issue_pv(t);
+      }
+      if (!ok) atomicExch(&failed, 1);
+    }
+  } else {  // ------------------------------------------------------- softmax and epilogue
+    // Two threads per query row: `part` 0 takes keys 0..63 of a tile and output columns
+    // 0..63, `part` 1 the rest; a warp reads the quarter of tensor memory its index allows.
+    const int quarter = warp & 3;
+    const int part = (warp - 2) >> 2;
+    const int row = quarter * 32 + lane;
+    const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
+    const int my_pos = pos0 + row;
+    const bool row_ok = row < n_rows;
+    uint8_t* p_row = base_ptr + 5 * TILE_BYTES + part * HALF_BYTES_TC + row * 128;
+    float o[64];
+#pragma unroll
+    for (int i = 0; i < 64; ++i) o[i] = 0.0f;
+    float m_run = -INFINITY, l_run = 0.0f, alpha_prev = 0.0f;
+    bool ok = true;
+
+    for (int t = 0; t < n_tiles; ++t) {  // no early exit: every thread meets every bar.sync
+      const int b = t & 1;
+      const int key0 = (tile_first + t) * TK + part * 64;
+      // interior tiles need no mask: every key is at or before every row and inside the window
+      const bool need_mask = (tile_first + t) * TK + TK - 1 > pos0 ||
+                             (window > 0 && (tile_first + t) * TK <= k_hi - window);
+      if (ok && !mbar_wait_bounded(s_full0 + 8 * b, (t >> 1) & 1)) ok = false;
+      tmem_fence_after();
+      uint32_t s0[32], s1[32];
+      const uint32_t s_addr = tmem_base + b * 128 + part * 64 + lane_off;
+      tmem_ld32(s_addr, s0);
+      tmem_ld32(s_addr + 32, s1);
+      tmem_ld_wait();
+      tmem_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(s_empty0 + 8 * b);  // S is in registers now
+      uint32_t keep0 = 0xffffffffu, keep1 = 0xffffffffu;
+      if (need_mask) {
+        keep0 = keep1 = 0;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int j0 = key0 + i, j1 = key0 + 32 + i;
+          if (row_ok && j0 <= my_pos && (window <= 0 || j0 > my_pos - window)) keep0 |= 1u << i;
+          if (row_ok && j1 <= my_pos && (window <= 0 || j1 > my_pos - window)) keep1 |= 1u << i;
+        }
+      }
+      float mx = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        const float a = (keep0 >> i & 1u) ? __uint_as_float(s0[i]) : -INFINITY;
+        const float c = (keep1 >> i & 1u) ? __uint_as_float(s1[i]) : -INFINITY;
+        mx = fmaxf(mx, fmaxf(a, c));
+      }
+      xmax[b][part][row] = mx;
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      mx = fmaxf(mx, xmax[b][part ^ 1][row]);
+      const float m_new = fmaxf(m_run, mx * scale_log2);
+      const float m_use = (m_new == -INFINITY) ? 0.0f : m_new;
+      const float alpha = ex2_approx(m_run - m_use);
+      // the P buffer must be free (PV of the previous tile has read it)
+      if (ok && t >= 1 && !mbar_wait_bounded(p_empty, (t - 1) & 1)) ok = false;
+      float sum = 0.0f;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {  // 16-byte chunks of 8 keys
+        float p[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int e = c * 8 + i;
+          const uint32_t sv = e < 32 ? s0[e & 31] : s1[e & 31];
+          const bool in = ((e < 32 ? keep0 : keep1) >> (e & 31)) & 1u;
+          p[i] = in ? ex2_approx(fmaf(__uint_as_float(sv), scale_log2, -m_use)) : 0.0f;
+          sum += p[i];
+        }
+        uint4 v;
+        __nv_bfloat162* hv = reinterpret_cast<__nv_bfloat162*>(&v);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) hv[i] = __floats2bfloat162_rn(p[2 * i], p[2 * i + 1]);
+        *reinterpret_cast<uint4*>(p_row + ((c ^ (row & 7)) << 4)) = v;
+      }
+      fence_proxy_async_smem();  // P was written with ordinary stores; the MMA reads it as an operand
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full);
+      // fold in the previous tile's PV, which is relative to the previous maximum
+      if (t >= 1) {
+        const int pb = (t - 1) & 1;
+        if (ok && !mbar_wait_bounded(o_full0 + 8 * pb, ((t - 1) >> 1) & 1)) ok = false;
+        tmem_fence_after();
+        const uint32_t o_addr = tmem_base + 256 + pb * 128 + part * 64 + lane_off;
+        uint32_t r0[32], r1[32];
+        tmem_ld32(o_addr, r0);
+        tmem_ld32(o_addr + 32, r1);
+        tmem_ld_wait();
+        tmem_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(o_empty0 + 8 * pb);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          o[i] = fmaf(o[i], alpha_prev, __uint_as_float(r0[i]));
+          o[32 + i] = fmaf(o[32 + i], alpha_prev, __uint_as_float(r1[i]));
+        }
+      }
+      alpha_prev = alpha;
+      l_run = l_run * alpha + sum;
+      m_run = m_new;
+    }
+    if (ok && n_tiles > 0) {  // the last tile's PV
+      const int pb = (n_tiles - 1) & 1;
+      if (mbar_wait_bounded(o_full0 + 8 * pb, ((n_tiles - 1) >> 1) & 1)) {
+        tmem_fence_after();
+        const uint32_t o_addr = tmem_base + 256 + pb * 128 + part * 64 + lane_off;
+        uint32_t r0[32], r1[32];
+        tmem_ld32(o_addr, r0);
+        tmem_ld32(o_addr + 32, r1);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          o[i] = fmaf(o[i], alpha_prev, __uint_as_float(r0[i]));
+          o[32 + i] = fmaf(o[32 + i], alpha_prev, __uint_as_float(r1[i]));
+        }
+      } else {
+        ok = false;
+      }
+    }
+    if (!ok) atomicExch(&failed, 1);
+    // the row's sum is the sum of its two threads' sums (the same maxima went into both)
+    xsum[part][row] = ok ? l_run : __int_as_float(0x7fc00000);
+    asm volatile("bar.sync 2, 256;" ::: "memory");
+    if (row_ok) {
+      const float inv = 1.0f / (xsum[0][row] + xsum[1][row]);
+      bf16* dst = out + (long long)(tok0 + row) * out_stride + (long long)h * HD + part * 64;
+#pragma unroll
+      for (int c = 0; c < 8; ++c) {
+        float w8[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) w8[i] = o[c * 8 + i] * inv;
+        store8<bf16>(dst + c * 8, w8);
+      }
+    }
+  }
+
+  tmem_fence_before();
+  __syncthreads();
+  pdl_trigger();
+  if (warp == 1) {
+    tmem_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;"
+                 ::"r"(tmem_base), "r"(512u) : "memory");
+  }
+}
+
+}  // namespace si
+
+SI_API int si_attn_prefill_tc_supported() { return 1; }
+
+// Attention for the 128-query tiles listed in tile_seq/tile_start (longest first).
+// q: the qkv buffer [n_tokens, q_stride] (query heads in its first columns).
+SI_API int si_attn_prefill_tc(const void* q, int q_stride, int n_tokens, const void* pool,
+                              int n_pages, const int* block_table, int table_stride,
+                              const int* cu_q, const int* positions, const int* tile_seq,
+                              const int* tile_start, int n_tiles, void* out, int out_stride,
+                              int n_q_heads, int n_kv_heads, int page_size, float scale, int window,
+                              cudaStream_t stream) {
+  using namespace si;
+  if (!q || !pool || !block_table || !cu_q || !positions || !tile_seq || !tile_start || !out)
+    return SI_ERR_ARG;
+  if (n_tiles < 0 || n_tokens <= 0 || n_pages <= 0 || n_q_heads <= 0 || n_kv_heads <= 0 ||
+      n_q_heads % n_kv_heads != 0 || table_stride <= 0 || q_stride % 8 != 0 || out_stride % 8 != 0)
+    return SI_ERR_ARG;
+  if (page_size < 8 || page_size > 64 || (page_size & (page_size - 1)) != 0) return SI_ERR_UNSUPPORTED;
+  if ((((uintptr_t)q | (uintptr_t)pool | (uintptr_t)out) & 15) != 0) return SI_ERR_ARG;
+  if (n_tiles > 65535) return SI_ERR_TOO_LARGE;
+  if (!(scale > 0.0f)) return SI_ERR_ARG;  // the row maximum is taken before scaling
+  if (n_tiles == 0) return SI_OK;
+  CUtensorMap q_map, kv_map;
+  if (!make_bf16_map(&q_map, q, n_tokens, n_q_heads * HD, q_stride, TQ)) return SI_ERR_UNSUPPORTED;
+  if (!make_bf16_map(&kv_map, pool, (long long)n_pages * 2 * n_kv_heads * page_size, HD, HD, page_size))
+    return SI_ERR_UNSUPPORTED;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, ATC_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    configured = true;
+  }
+  dim3 grid(n_q_heads, n_tiles);
+  SI_LAUNCH(attn_prefill_tc_kernel, grid, ATC_THREADS, ATC_SMEM, stream, q_map, kv_map, block_table,
+            table_stride, cu_q, positions, tile_seq, tile_start, (bf16*)out, out_stride, n_q_heads,
+            n_kv_heads, page_size, scale * LOG2E_TC, window);
+  return SI_OK;
+}
+
+#else  // other head sizes: the mma.sync kernel of attention_mma.cu serves them
+
+#include "common.cuh"
+SI_API int si_attn_prefill_tc_supported() { return 0; }
+SI_API int si_attn_prefill_tc(const void*, int, int, const void*, int, const int*, int, const int*,
+                              const int*, const int*, const int*, int, void*, int, int, int, int,
+                              float, int, cudaStream_t) {
+  return SI_ERR_UNSUPPORTED;
+}
+
+#endif

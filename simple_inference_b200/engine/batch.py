@@ -31,7 +31,8 @@ import torch
 
 from ..cache.manager import CacheManager, pages_for
 
-QUERY_TILE = 64  # query rows per block of the tensor-core prefill kernel
+QUERY_TILE = 64  # query rows per block of the mma.sync prefill kernel
+WIDE_TILE = 128  # query rows per block of the tcgen05 prefill kernel
 
 
 @dataclass
@@ -115,6 +116,9 @@ class StepContext:
     n_tiles: int
     tile_pairs: torch.Tensor
     n_pairs: int
+    wide_seq: torch.Tensor    # the same portions cut into WIDE_TILE-query tiles, longest first
+    wide_start: torch.Tensor
+    n_wide: int
     max_kv_len: int
     max_q_len: int
     max_seqs: int
@@ -151,6 +155,8 @@ class BatchBuilder:
         seg("tile_seq", self.max_tiles)
         seg("tile_start", self.max_tiles)
         seg("tile_pairs", self.max_tiles + 1)
+        seg("wide_seq", self.max_tiles)
+        seg("wide_start", self.max_tiles)
         for g in range(self.n_groups):
             seg(f"block_table{g}", max_seqs * self.table_len[g])
         seg("token_ids", max_tokens)
@@ -206,6 +212,7 @@ class BatchBuilder:
         tile_start = self._h("tile_start")
         tile_pairs = self._h("tile_pairs")
         tile_work: list[int] = []
+        wide: list[tuple[int, int, int]] = []  # (keys its last row sees, sequence, first row)
         tables = [self._h(f"block_table{g}").reshape(self.max_seqs, self.table_len[g])
                   for g in range(self.n_groups)]
         kv_slots = [self._h(f"kv_slots{g}") for g in range(self.n_groups)]
@@ -266,6 +273,8 @@ class BatchBuilder:
                     tile_start[n_tiles] = q0
                     tile_work.append(start + min(q0 + QUERY_TILE, n))  # keys its last row sees
                     n_tiles += 1
+                for q0 in range(0, n, WIDE_TILE):
+                    wide.append((start + min(q0 + WIDE_TILE, n), s, q0))
             q_lens.append(n); kv_lens.append(end)
             t += n
             cu_q[s + 1] = t
@@ -284,6 +293,12 @@ class BatchBuilder:
             cu_q[s + 1] = t
         S += pad; N = t
         n_pairs = pair_tiles(tile_work, tile_pairs)
+        if wide:
+            wide.sort(key=lambda w: -w[0])
+            ws_, wq_ = self._h("wide_seq"), self._h("wide_start")
+            for i, (_, s, q0) in enumerate(wide):
+                ws_[i] = s
+                wq_[i] = q0
 
         self.dev.copy_(self.host, non_blocking=True)
         if self._copied is not None:
@@ -301,6 +316,8 @@ class BatchBuilder:
             logit_rows=self._d("logit_rows", r),
             single_seqs=self._d("single_seqs", n_single), n_single=n_single,
             tile_seq=self._d("tile_seq", n_tiles), tile_start=self._d("tile_start", n_tiles),
-            n_tiles=n_tiles, tile_pairs=self._d("tile_pairs", 2 * n_pairs), n_pairs=n_pairs, max_kv_len=max(kv_lens) if kv_lens else 0,
+            n_tiles=n_tiles, tile_pairs=self._d("tile_pairs", 2 * n_pairs), n_pairs=n_pairs,
+            wide_seq=self._d("wide_seq", len(wide)), wide_start=self._d("wide_start", len(wide)),
+            n_wide=len(wide), max_kv_len=max(kv_lens) if kv_lens else 0,
             max_q_len=max(q_lens) if q_lens else 0, max_seqs=self.max_seqs, ws=ws, q_lens=q_lens, kv_lens=kv_lens,
         )

@@ -53,6 +53,9 @@ def core() -> ctypes.CDLL:
     return _core_lib
 
 
+ATTENTION_SOURCES = ["attention_mma.cu", "attention_tc.cu"]
+
+
 def attention_library(head_dim: int) -> ctypes.CDLL:
     """Tensor-core attention kernels are compiled for one head size at a time."""
     lib = _attention_libs.get(head_dim)
@@ -61,7 +64,7 @@ def attention_library(head_dim: int) -> ctypes.CDLL:
             raise KernelError(
                 f"head_dim {head_dim}: the attention kernels take multiples of 16 from 16 to 256"
             )
-        lib = load_library(f"si_attn_d{head_dim}", ["attention_mma.cu"],
+        lib = load_library(f"si_attn_d{head_dim}", ATTENTION_SOURCES,
                            [f"-DSI_HEAD_DIM={head_dim}"])
         _attention_libs[head_dim] = lib
     return lib
@@ -362,7 +365,10 @@ def paged_attention(q: torch.Tensor, pool: torch.Tensor, ctx, group: int, out: t
         raise KernelError("attention: pool/out shape or dtype does not fit")
     lib = attention_library(head_dim)
     win = int(window or 0)
-    if ctx.n_tiles:
+    if ctx.n_tiles and wide_prefill_fits(ctx, head_dim, page_size):
+        attention_prefill_wide(q, pool, ctx, group, out, num_q_heads, num_kv_heads, head_dim, scale,
+                               window)
+    elif ctx.n_tiles:
         _check(lib.si_attn_prefill(
             _p(q), q.stride(0), _p(pool), _p(table), table.stride(0), _p(ctx.cu_q),
             _p(ctx.positions), _p(ctx.tile_seq), _p(ctx.tile_start), _p(ctx.tile_pairs),
@@ -381,6 +387,40 @@ def paged_attention(q: torch.Tensor, pool: torch.Tensor, ctx, group: int, out: t
             _p(ctx.positions), _p(ctx.single_seqs), ctx.n_single, _p(out), out.stride(0),
             _p(scratch), num_q_heads, num_kv_heads, page_size, _c_float(scale), win, n_splits,
             _stream()), "attn_decode", kernels=2 if n_splits > 1 else 1)
+    return out
+
+
+WIDE_MIN_QUERIES = 64  # shorter portions stay on the 64-query mma.sync tiles
+
+
+def wide_prefill_fits(ctx, head_dim: int, page_size: int) -> bool:
+    """Whether the tcgen05 prefill kernel takes this step's portions: it is written for heads
+    of 128 and pages of 8, 16, 32 or 64 tokens, and pays off from 64 queries a portion."""
+    return head_dim == 128 and page_size in (8, 16, 32, 64) and \
+        getattr(ctx, "n_wide", 0) > 0 and getattr(ctx, "max_q_len", 0) >= WIDE_MIN_QUERIES
+
+
+def attention_prefill_wide(q: torch.Tensor, pool: torch.Tensor, ctx, group: int, out: torch.Tensor,
+                           num_q_heads: int, num_kv_heads: int, head_dim: int, scale: float,
+                           window: int | None) -> torch.Tensor:
+    """The tcgen05 prefill kernel on the step's 128-query tiles (``ctx.wide_seq/wide_start``).
+
+    ``q`` is the query part of the fused projection output, a view with its row stride.
+    """
+    table = ctx.block_tables[group]
+    _dev(pool, table, out)
+    page_size = pool.shape[3]
+    if not q.is_cuda or q.dtype != torch.bfloat16 or pool.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or \
+            q.stride(1) != 1 or tuple(pool.shape[1:]) != (2, num_kv_heads, page_size, head_dim):
+        raise KernelError("attention_prefill_wide: bfloat16 q, pool and out of fitting shapes")
+    lib = attention_library(head_dim)
+    if not lib.si_attn_prefill_tc_supported():
+        raise KernelError(f"attention_prefill_wide: no tcgen05 kernel for head size {head_dim}")
+    _check(lib.si_attn_prefill_tc(
+        _p(q), q.stride(0), q.shape[0], _p(pool), pool.shape[0], _p(table), table.stride(0),
+        _p(ctx.cu_q), _p(ctx.positions), _p(ctx.wide_seq), _p(ctx.wide_start), ctx.n_wide, _p(out),
+        out.stride(0), num_q_heads, num_kv_heads, page_size, _c_float(scale), int(window or 0),
+        _stream()), "attn_prefill_tc")
     return out
 
 
@@ -408,4 +448,4 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
 
 __all__ = ["KernelError", "KernelBuildError", "embed_gather", "rmsnorm", "swiglu", "linear", "linear_swiglu", "linear_tc",
            "can_fuse_swiglu", "check_status", "status_tensor",
-           "rope_kv_store", "attention_generic", "paged_attention", "plan_kv_splits", "sample", "core", "attention_library"]
+           "rope_kv_store", "attention_generic", "paged_attention", "attention_prefill_wide", "wide_prefill_fits", "plan_kv_splits", "sample", "core", "attention_library"]

@@ -115,6 +115,8 @@ def paged_case(lens_q, starts, ps, hq, hkv, d, dt, seed=0):
     from simple_inference_b200.engine.batch import Workspace, pair_tiles
     pairs = [0] * (len(tile_seq) + 2)
     n_pairs = pair_tiles([starts[s] + min(q0 + 64, lens_q[s]) for s, q0 in zip(tile_seq, tile_start)], pairs)
+    wide = sorted(((starts[s] + min(q0 + 128, lens_q[s]), s, q0) for s in range(S)
+                   if lens_q[s] > 1 for q0 in range(0, lens_q[s], 128)), key=lambda w: -w[0])
     I = lambda x: torch.tensor(x, dtype=torch.int32, device=dev())  # noqa: E731
     pool = torch.randn(P + 1, 2, hkv, ps, d, device=dev(), generator=g).to(dt)
     qkv = torch.randn(N, (hq + 2 * hkv) * d, device=dev(), generator=g).to(dt)
@@ -122,7 +124,8 @@ def paged_case(lens_q, starts, ps, hq, hkv, d, dt, seed=0):
         block_tables=[bt.to(dev())], tok_seq=I(tok_seq), positions=I(pos), cu_q=I(cu),
         kv_slots=[I(slots)], single_seqs=I(single), n_single=len(single), tile_seq=I(tile_seq),
         tile_start=I(tile_start), n_tiles=len(tile_seq), tile_pairs=I(pairs[:2 * n_pairs]),
-        n_pairs=n_pairs, max_kv_len=max(kv), max_seqs=S,
+        n_pairs=n_pairs, wide_seq=I([w[1] for w in wide]), wide_start=I([w[2] for w in wide]),
+        n_wide=len(wide), max_kv_len=max(kv), max_q_len=max(lens_q), max_seqs=S,
         ws=Workspace(dev(), N))
     return qkv, pool, ctx, N
 
@@ -195,6 +198,57 @@ def test_tensor_core_attention_bfloat16(ops, monkeypatch, what, lens, starts, ps
                                ctx.positions, ref, hq, hkv, d, 1 / math.sqrt(d), window)
     # the kernel rounds P to bfloat16 before P V and the result once: a few 1e-3 relative
     assert (out.float() - ref).abs().max() < 2e-2
+
+
+WIDE_CASES = [
+    ("one full tile", [128], [0], 16, 4, 2, None),
+    ("short tile", [70], [0], 16, 4, 2, None),
+    ("six key tiles, ragged end", [700], [0], 16, 6, 3, None),
+    ("deep in a context, page of 8", [130, 66], [333, 1500], 8, 4, 1, None),
+    ("page of 64", [200], [77], 64, 2, 2, None),
+    ("page of 32, three portions", [64, 300, 2], [0, 31, 900], 32, 3, 3, None),
+    ("window inside one tile", [300], [100], 16, 4, 2, 40),
+    ("window over several tiles", [260], [1000], 16, 2, 1, 300),
+    ("twenty-four heads", [256], [0], 16, 24, 8, None),
+]
+
+
+@pytest.mark.parametrize("what,lens,starts,ps,hq,hkv,window", WIDE_CASES,
+                         ids=[c[0] for c in WIDE_CASES])
+def test_tcgen05_prefill_attention(ops, what, lens, starts, ps, hq, hkv, window):
+    d = 128
+    qkv, pool, ctx, n = paged_case(lens, starts, ps, hq, hkv, d, torch.bfloat16, seed=3)
+    assert ops.wide_prefill_fits(ctx, d, ps)
+    out = torch.zeros(n, hq * d, device=dev(), dtype=torch.bfloat16)
+    ops.attention_prefill_wide(qkv[:, :hq * d], pool, ctx, 0, out, hq, hkv, d, 1 / math.sqrt(d),
+                               window)
+    ref = torch.zeros(n, hq * d, device=dev())
+    twin_ops.attention_generic(qkv.float(), pool.float(), ctx.block_tables[0], ctx.tok_seq,
+                               ctx.positions, ref, hq, hkv, d, 1 / math.sqrt(d), window)
+    assert bool(torch.isfinite(out.float()).all()), "a bounded wait ran out (NaN marks it)"
+    assert (out.float() - ref).abs().max() < 2e-2
+
+
+def test_tcgen05_prefill_finds_one_far_key(ops):
+    """One key per query head, far back and on a page of its own, matches 30 times better
+    than the rest: every row's output must be that key's value (7)."""
+    hq, hkv, d, ps = 4, 2, 128, 16
+    qkv, pool, ctx, n = paged_case([200, 129], [900, 300], ps, hq, hkv, d, torch.bfloat16, seed=5)
+    pool.mul_(0.05)
+    table = ctx.block_tables[0]
+    for seq, far in ((0, 437), (1, 23)):
+        page, off = int(table[seq, far // ps]), far % ps
+        toks = (ctx.tok_seq == seq).nonzero().flatten()
+        for h in range(hq):
+            kvh = h // (hq // hkv)
+            pool[page, 0, kvh, off, h * 3] = 30.0
+            key = torch.zeros(d, device=dev())
+            key[h * 3] = 30.0
+            qkv[toks, h * d:(h + 1) * d] = key.bfloat16()
+        pool[page, 1, :, off, :] = 7.0
+    out = torch.zeros(n, hq * d, device=dev(), dtype=torch.bfloat16)
+    ops.attention_prefill_wide(qkv[:, :hq * d], pool, ctx, 0, out, hq, hkv, d, 1 / math.sqrt(d), None)
+    assert (out.float() - 7.0).abs().max() < 0.1
 
 
 def test_attention_finds_one_far_key_among_hundreds(ops):
