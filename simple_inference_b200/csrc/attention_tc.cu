@@ -10,15 +10,17 @@
 //                      lane per page) into a two-stage ring; mbarriers count the bytes.
 //   warp 1, one lane   MMA issuer: S = Q K^T (M128 N128, eight K16 steps; Q and K are
 //                      K-major) into one of two S buffers in tensor memory, and
-//                      PV = P V (P is K-major in shared memory, V is MN-major: its rows are
-//                      keys) into one of two output buffers.  S of the next tile is issued
+//                      PV = P V (P is read from tensor memory, where the softmax warps put it
+//                      over the S it came from; V is MN-major: its rows are keys) into one
+//                      of two output buffers.  S of the next tile is issued
 //                      before PV of this one, so the tensor core works while softmax runs.
 //   warps 2..9         softmax, two threads per query row (64 keys and 64 output columns
 //                      each): read S with tcgen05.ld, trade the row maximum through shared
 //                      memory, mask edge tiles by absolute position, online softmax in
 //                      float32 (kernels/attention_kernel.py:231-241), round P to bfloat16
-//                      (:240) and write it to shared memory in the operand layout; read each
-//                      tile's PV from tensor memory and keep O = O*alpha + PV in registers;
+//                      (:240) and store it to tensor memory as the next product's A operand;
+//                      read each tile's PV from tensor memory and keep O = O*alpha + PV in
+//                      registers (two-wide float32 instructions);
 //                      at the end divide by l and store.
 // Every mbarrier wait is bounded; a block whose wait runs out writes NaN to its outputs.
 #include "tcgen05.cuh"
@@ -36,13 +38,37 @@ constexpr int TQ = 128, TK = 128, HD = 128;
 constexpr uint32_t HALF_BYTES_TC = 128 * 128;        // 128 rows x 64 bf16
 constexpr uint32_t TILE_BYTES = 2 * HALF_BYTES_TC;   // 128 x 128 bf16 = 32 KiB
 constexpr int ATC_THREADS = 320;  // producer warp, MMA warp, eight softmax warps
-constexpr uint32_t ATC_SMEM = 1024 + 6 * TILE_BYTES + 256;  // Q, K0, K1, V0, V1, P + barriers
+constexpr uint32_t ATC_SMEM = 1024 + 5 * TILE_BYTES + 256;  // Q, K0, K1, V0, V1 + barriers
 constexpr float LOG2E_TC = 1.4426950408889634f;
 
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// O = O * alpha + PV for this thread's 64 output columns of buffer `o_addr`
+__device__ __forceinline__ void fold_pv(float2 (&o)[32], float alpha, uint32_t o_addr) {
+  uint32_t r0[32], r1[32];
+  tmem_ld32(o_addr, r0);
+  tmem_ld32(o_addr + 32, r1);
+  tmem_ld_wait();
+  const float2 a2 = make_float2(alpha, alpha);
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    o[i] = __ffma2_rn(o[i], a2, make_float2(__uint_as_float(r0[2 * i]), __uint_as_float(r0[2 * i + 1])));
+    o[16 + i] = __ffma2_rn(o[16 + i], a2,
+                           make_float2(__uint_as_float(r1[2 * i]), __uint_as_float(r1[2 * i + 1])));
+  }
 }
 
 __global__ void __launch_bounds__(ATC_THREADS, 1)
@@ -57,14 +83,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - raw);
-  const uint32_t sQ = base, sK0 = base + TILE_BYTES, sV0 = base + 3 * TILE_BYTES,
-                 sP = base + 5 * TILE_BYTES;
-  const uint32_t bars = base + 6 * TILE_BYTES;
+  const uint32_t sQ = base, sK0 = base + TILE_BYTES, sV0 = base + 3 * TILE_BYTES;
+  const uint32_t bars = base + 5 * TILE_BYTES;
   // barriers, 8 bytes each
   const uint32_t q_full = bars, kv_full0 = bars + 8, kv_empty0 = bars + 24, s_full0 = bars + 40,
-                 s_empty0 = bars + 56, p_full = bars + 72, p_empty = bars + 80,
-                 o_full0 = bars + 88, o_empty0 = bars + 104, tmem_slot = bars + 120;
-  volatile uint32_t* tmem_slot_ptr = reinterpret_cast<volatile uint32_t*>(base_ptr + 6 * TILE_BYTES + 120);
+                 p_full0 = bars + 56, o_full0 = bars + 72, o_empty0 = bars + 88,
+                 tmem_slot = bars + 104;
+  volatile uint32_t* tmem_slot_ptr =
+      reinterpret_cast<volatile uint32_t*>(base_ptr + 5 * TILE_BYTES + 104);
   __shared__ int failed;
   __shared__ float xmax[2][2][TQ];  // [tile parity][part][row]: the two threads of a row trade maxima
   __shared__ float xsum[2][TQ];
@@ -78,12 +104,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
       mbar_init(kv_full0 + 8 * i, 1);
       mbar_init(kv_empty0 + 8 * i, 1);
       mbar_init(s_full0 + 8 * i, 1);
-      mbar_init(s_empty0 + 8 * i, 8);
+      mbar_init(p_full0 + 8 * i, 8);
       mbar_init(o_full0 + 8 * i, 1);
       mbar_init(o_empty0 + 8 * i, 8);
     }
-    mbar_init(p_full, 8);
-    mbar_init(p_empty, 1);
     mbar_init_fence();
   }
   if (warp == 1) {
@@ -118,6 +142,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
   const int tile_first = k_lo / TK, tile_last = k_hi / TK;
   const int n_tiles = tile_last - tile_first + 1;
   const int* table = block_table + (long long)seq * table_stride;
+
+  // Tensor memory: S of tile t in columns [128 b, 128 b + 128) with b = t & 1; P of tile t,
+  // bfloat16 pairs, over the first 64 columns of the same buffer once S has been read;
+  // P V of tile t in columns [256 + 128 b, 256 + 128 b + 128).
 
   if (warp == 0) {  // ----------------------------------------------------------- TMA producer
     // Lane i looks up and fetches page i of a key tile, so the table reads of a tile are in
@@ -161,13 +189,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
     }
   } else if (warp == 1) {
     if (lane == 0) {  // --------------------------------------------------------- MMA issuer
+      // Issue order S(0), S(1), PV(0), S(2), PV(1), ...  The tensor core runs them in that
+      // order, so S(t+2) overwrites its buffer only after PV(t) has read P(t) from it, and
+      // PV(t) is issued only after the softmax warps have read S(t) and written P(t).
       constexpr uint32_t idesc_s = umma_idesc(TQ, TK, false);   // Q K^T: both K-major
       constexpr uint32_t idesc_o = umma_idesc(TQ, HD, true);    // P V: V is MN-major
       bool ok = mbar_wait_bounded(q_full, 0);
       auto issue_s = [&](int t) {
         const int b = t & 1;
         if (!mbar_wait_bounded(kv_full0 + 8 * b, (t >> 1) & 1)) return false;
-        if (t >= 2 && !mbar_wait_bounded(s_empty0 + 8 * b, ((t >> 1) - 1) & 1)) return false;
         tmem_fence_after();
         const uint32_t kbase = sK0 + b * TILE_BYTES;
 #pragma unroll
@@ -181,19 +211,17 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
       };
       auto issue_pv = [&](int t) {
         const int b = t & 1;
-        if (!mbar_wait_bounded(p_full, t & 1)) return false;
+        if (!mbar_wait_bounded(p_full0 + 8 * b, (t >> 1) & 1)) return false;
         if (t >= 2 && !mbar_wait_bounded(o_empty0 + 8 * b, ((t >> 1) - 1) & 1)) return false;
         tmem_fence_after();
         const uint32_t vbase = sV0 + b * TILE_BYTES;
 #pragma unroll
-        for (int k = 0; k < TK / 16; ++k) {  // 16 keys per step
-          const uint64_t da = umma_desc(sP + (k >> 2) * HALF_BYTES_TC + (k & 3) * 32);
-          const uint64_t db = umma_desc_mn(vbase + k * 2048, HALF_BYTES_TC);  // 16 keys = 2 groups of 8 rows
-          umma_bf16(tmem_base + 256 + b * 128, da, db, idesc_o, k != 0 ? 1u : 0u);
+        for (int k = 0; k < TK / 16; ++k) {  // 16 keys per step: 8 columns of packed P, 2048 bytes of V
+          umma_bf16_ts(tmem_base + 256 + b * 128, tmem_base + b * 128 + k * 8,
+                       umma_desc_mn(vbase + k * 2048, HALF_BYTES_TC), idesc_o, k != 0 ? 1u : 0u);
         }
         umma_commit(o_full0 + 8 * b);
         umma_commit(kv_empty0 + 8 * b);
-        umma_commit(p_empty);
         return true;
       };
       if (ok) ok = issue_s(0);
@@ -212,10 +240,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
     const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
     const int my_pos = pos0 + row;
     const bool row_ok = row < n_rows;
-    uint8_t* p_row = base_ptr + 5 * TILE_BYTES + part * HALF_BYTES_TC + row * 128;
-    float o[64];
+    float2 o[32];
 #pragma unroll
-    for (int i = 0; i < 64; ++i) o[i] = 0.0f;
+    for (int i = 0; i < 32; ++i) o[i] = make_float2(0.0f, 0.0f);
     float m_run = -INFINITY, l_run = 0.0f, alpha_prev = 0.0f;
     bool ok = true;
 
@@ -232,95 +259,61 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
       tmem_ld32(s_addr, s0);
       tmem_ld32(s_addr + 32, s1);
       tmem_ld_wait();
-      tmem_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(s_empty0 + 8 * b);  // S is in registers now
-      uint32_t keep0 = 0xffffffffu, keep1 = 0xffffffffu;
       if (need_mask) {
-        keep0 = keep1 = 0;
 #pragma unroll
         for (int i = 0; i < 32; ++i) {
           const int j0 = key0 + i, j1 = key0 + 32 + i;
-          if (row_ok && j0 <= my_pos && (window <= 0 || j0 > my_pos - window)) keep0 |= 1u << i;
-          if (row_ok && j1 <= my_pos && (window <= 0 || j1 > my_pos - window)) keep1 |= 1u << i;
+          if (!(row_ok && j0 <= my_pos && (window <= 0 || j0 > my_pos - window))) s0[i] = 0xff800000u;
+          if (!(row_ok && j1 <= my_pos && (window <= 0 || j1 > my_pos - window))) s1[i] = 0xff800000u;
         }
       }
-      float mx = -INFINITY;
+      float mx = fmaxf(__uint_as_float(s0[0]), __uint_as_float(s1[0]));
 #pragma unroll
-      for (int i = 0; i < 32; ++i) {
-        const float a = (keep0 >> i & 1u) ? __uint_as_float(s0[i]) : -INFINITY;
-        const float c = (keep1 >> i & 1u) ? __uint_as_float(s1[i]) : -INFINITY;
-        mx = fmaxf(mx, fmaxf(a, c));
-      }
+      for (int i = 1; i < 32; ++i) mx = fmax3(mx, __uint_as_float(s0[i]), __uint_as_float(s1[i]));
       xmax[b][part][row] = mx;
-      asm volatile("bar.sync 1, 256;" ::: "memory");
+      asm volatile("bar.sync 1, 256;" ::: "memory");  // also: both parts hold their S in registers
       mx = fmaxf(mx, xmax[b][part ^ 1][row]);
       const float m_new = fmaxf(m_run, mx * scale_log2);
       const float m_use = (m_new == -INFINITY) ? 0.0f : m_new;
       const float alpha = ex2_approx(m_run - m_use);
-      // the P buffer must be free (PV of the previous tile has read it)
-      if (ok && t >= 1 && !mbar_wait_bounded(p_empty, (t - 1) & 1)) ok = false;
-      float sum = 0.0f;
+      // P = exp2(S * scale - m): masked entries are -inf and give 0
+      const float2 sc2 = make_float2(scale_log2, scale_log2), nm2 = make_float2(-m_use, -m_use);
+      float2 acc = make_float2(0.0f, 0.0f);
+      uint32_t pk[32];
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {  // 16-byte chunks of 8 keys
-        float p[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int e = c * 8 + i;
-          const uint32_t sv = e < 32 ? s0[e & 31] : s1[e & 31];
-          const bool in = ((e < 32 ? keep0 : keep1) >> (e & 31)) & 1u;
-          p[i] = in ? ex2_approx(fmaf(__uint_as_float(sv), scale_log2, -m_use)) : 0.0f;
-          sum += p[i];
-        }
-        uint4 v;
-        __nv_bfloat162* hv = reinterpret_cast<__nv_bfloat162*>(&v);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) hv[i] = __floats2bfloat162_rn(p[2 * i], p[2 * i + 1]);
-        *reinterpret_cast<uint4*>(p_row + ((c ^ (row & 7)) << 4)) = v;
+      for (int i = 0; i < 16; ++i) {
+        float2 x = __ffma2_rn(make_float2(__uint_as_float(s0[2 * i]), __uint_as_float(s0[2 * i + 1])), sc2, nm2);
+        float2 y = __ffma2_rn(make_float2(__uint_as_float(s1[2 * i]), __uint_as_float(s1[2 * i + 1])), sc2, nm2);
+        x.x = ex2_approx(x.x); x.y = ex2_approx(x.y);
+        y.x = ex2_approx(y.x); y.y = ex2_approx(y.y);
+        acc = __fadd2_rn(acc, __fadd2_rn(x, y));
+        pk[i] = pack_bf16(x.x, x.y);
+        pk[16 + i] = pack_bf16(y.x, y.y);
       }
-      fence_proxy_async_smem();  // P was written with ordinary stores; the MMA reads it as an operand
+      tmem_st32(tmem_base + b * 128 + part * 32 + lane_off, pk);
+      tmem_st_wait();
+      tmem_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(p_full);
+      if (lane == 0) mbar_arrive(p_full0 + 8 * b);
       // fold in the previous tile's PV, which is relative to the previous maximum
       if (t >= 1) {
         const int pb = (t - 1) & 1;
         if (ok && !mbar_wait_bounded(o_full0 + 8 * pb, ((t - 1) >> 1) & 1)) ok = false;
         tmem_fence_after();
-        const uint32_t o_addr = tmem_base + 256 + pb * 128 + part * 64 + lane_off;
-        uint32_t r0[32], r1[32];
-        tmem_ld32(o_addr, r0);
-        tmem_ld32(o_addr + 32, r1);
-        tmem_ld_wait();
+        fold_pv(o, alpha_prev, tmem_base + 256 + pb * 128 + part * 64 + lane_off);
         tmem_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(o_empty0 + 8 * pb);
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          o[i] = fmaf(o[i], alpha_prev, __uint_as_float(r0[i]));
-          o[32 + i] = fmaf(o[32 + i], alpha_prev, __uint_as_float(r1[i]));
-        }
       }
       alpha_prev = alpha;
-      l_run = l_run * alpha + sum;
+      l_run = l_run * alpha + (acc.x + acc.y);
       m_run = m_new;
     }
-    if (ok && n_tiles > 0) {  // the last tile's PV
+    if (n_tiles > 0) {  // the last tile's PV
       const int pb = (n_tiles - 1) & 1;
-      if (mbar_wait_bounded(o_full0 + 8 * pb, ((n_tiles - 1) >> 1) & 1)) {
-        tmem_fence_after();
-        const uint32_t o_addr = tmem_base + 256 + pb * 128 + part * 64 + lane_off;
-        uint32_t r0[32], r1[32];
-        tmem_ld32(o_addr, r0);
-        tmem_ld32(o_addr + 32, r1);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          o[i] = fmaf(o[i], alpha_prev, __uint_as_float(r0[i]));
-          o[32 + i] = fmaf(o[32 + i], alpha_prev, __uint_as_float(r1[i]));
-        }
-      } else {
-        ok = false;
-      }
+      if (ok && !mbar_wait_bounded(o_full0 + 8 * pb, ((n_tiles - 1) >> 1) & 1)) ok = false;
+      tmem_fence_after();
+      fold_pv(o, alpha_prev, tmem_base + 256 + pb * 128 + part * 64 + lane_off);
     }
     if (!ok) atomicExch(&failed, 1);
     // the row's sum is the sum of its two threads' sums (the same maxima went into both)
@@ -333,7 +326,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
       for (int c = 0; c < 8; ++c) {
         float w8[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) w8[i] = o[c * 8 + i] * inv;
+        for (int i = 0; i < 4; ++i) {
+          w8[2 * i] = o[c * 4 + i].x * inv;
+          w8[2 * i + 1] = o[c * 4 + i].y * inv;
+        }
         store8<bf16>(dst + c * 8, w8);
       }
     }
