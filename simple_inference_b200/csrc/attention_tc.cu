@@ -7,7 +7,8 @@
 //   warp 0             TMA producer: the Q tile once (two 64-column halves, straight from
 //                      the qkv buffer), then per key tile the K and V rows of its pages
 //                      (cp.async.bulk.tensor boxes of page_size x 64, 128-byte swizzle; one
-//                      lane per page) into a two-stage ring; mbarriers count the bytes.
+//                      lane per page) into a ring of slots that K and V tiles share, in the
+//                      order the products need them; mbarriers count the bytes.
 //   warp 1, one lane   MMA issuer: S = Q K^T (M128 N128, eight K16 steps; Q and K are
 //                      K-major) into one of two S buffers in tensor memory, and
 //                      PV = P V (P is read from tensor memory, where the softmax warps put it
@@ -38,7 +39,13 @@ constexpr int TQ = 128, TK = 128, HD = 128;
 constexpr uint32_t HALF_BYTES_TC = 128 * 128;        // 128 rows x 64 bf16
 constexpr uint32_t TILE_BYTES = 2 * HALF_BYTES_TC;   // 128 x 128 bf16 = 32 KiB
 constexpr int ATC_THREADS = 320;  // producer warp, MMA warp, eight softmax warps
-constexpr uint32_t ATC_SMEM = 1024 + 5 * TILE_BYTES + 256;  // Q, K0, K1, V0, V1 + barriers
+constexpr int RING = 5;           // K and V tiles share one ring of 32 KiB slots
+constexpr uint32_t ATC_SMEM = 1024 + (1 + RING) * TILE_BYTES + 256;  // Q, the ring, barriers
+
+// Tiles enter the ring in the order the tensor core needs them: K0, K1, V0, K2, V1, ...,
+// K(n-1), V(n-2), V(n-1).
+__device__ __forceinline__ int k_item(int t) { return t == 0 ? 0 : 2 * t - 1; }
+__device__ __forceinline__ int v_item(int t, int n) { return t < n - 1 ? 2 * t + 2 : 2 * t + 1; }
 constexpr float LOG2E_TC = 1.4426950408889634f;
 
 __device__ __forceinline__ float ex2_approx(float x) {
@@ -83,14 +90,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
   const uint32_t raw = smem_u32(smem_raw);
   const uint32_t base = (raw + 1023u) & ~1023u;
   uint8_t* base_ptr = smem_raw + (base - raw);
-  const uint32_t sQ = base, sK0 = base + TILE_BYTES, sV0 = base + 3 * TILE_BYTES;
-  const uint32_t bars = base + 5 * TILE_BYTES;
+  const uint32_t sQ = base, ring = base + TILE_BYTES;
+  const uint32_t bars = base + (1 + RING) * TILE_BYTES;
   // barriers, 8 bytes each
-  const uint32_t q_full = bars, kv_full0 = bars + 8, kv_empty0 = bars + 24, s_full0 = bars + 40,
-                 p_full0 = bars + 56, o_full0 = bars + 72, o_empty0 = bars + 88,
-                 tmem_slot = bars + 104;
+  const uint32_t q_full = bars, s_full0 = bars + 8, p_full0 = bars + 24, o_full0 = bars + 40,
+                 o_empty0 = bars + 56, tmem_slot = bars + 72, slot_full0 = bars + 80,
+                 slot_empty0 = slot_full0 + 8 * RING;
   volatile uint32_t* tmem_slot_ptr =
-      reinterpret_cast<volatile uint32_t*>(base_ptr + 5 * TILE_BYTES + 104);
+      reinterpret_cast<volatile uint32_t*>(base_ptr + (1 + RING) * TILE_BYTES + 72);
   __shared__ int failed;
   __shared__ float xmax[2][2][TQ];  // [tile parity][part][row]: the two threads of a row trade maxima
   __shared__ float xsum[2][TQ];
@@ -100,9 +107,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
   if (threadIdx.x == 0) {
     failed = 0;
     mbar_init(q_full, 1);
+    for (int i = 0; i < RING; ++i) {
+      mbar_init(slot_full0 + 8 * i, 1);
+      mbar_init(slot_empty0 + 8 * i, 1);
+    }
     for (int i = 0; i < 2; ++i) {
-      mbar_init(kv_full0 + 8 * i, 1);
-      mbar_init(kv_empty0 + 8 * i, 1);
       mbar_init(s_full0 + 8 * i, 1);
       mbar_init(p_full0 + 8 * i, 8);
       mbar_init(o_full0 + 8 * i, 1);
@@ -116,10 +125,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     tmem_fence_before();
   }
-  // K/V stages start as zeros: rows of pages that are not loaded meet P = 0 and must be finite
+  // The ring starts as zeros: rows of pages that are not loaded meet P = 0 and must be finite
+  // (later a slot holds an earlier tile's keys or values, which are finite too)
   {
     uint4* z = reinterpret_cast<uint4*>(base_ptr + TILE_BYTES);
-    for (int i = threadIdx.x; i < (int)(4 * TILE_BYTES / 16); i += ATC_THREADS)
+    for (int i = threadIdx.x; i < (int)(RING * TILE_BYTES / 16); i += ATC_THREADS)
       z[i] = make_uint4(0, 0, 0, 0);
   }
   fence_proxy_async_smem();
@@ -156,35 +166,39 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
       tma_load_2d(sQ + HALF_BYTES_TC, &q_map, q_full, h * HD + 64, tok0);
     }
     const int pages_per_tile = TK / page_size;  // at most 16
+    const int n_items = 2 * n_tiles;
+    // item i: keys (odd i, and i = 0) or values of which tile
+    auto tile_of = [&](int i, bool& is_v) {
+      is_v = i != 0 && ((i & 1) == 0 || i == n_items - 1);
+      return i == 0 ? 0 : (is_v ? (i == n_items - 1 ? n_tiles - 1 : (i - 2) / 2) : (i + 1) / 2);
+    };
     auto page_of = [&](int t) {
       const int j0 = (tile_first + t) * TK + lane * page_size;
       const bool wanted = lane < pages_per_tile && j0 <= k_hi && j0 + page_size - 1 >= k_lo;
       return wanted ? table[j0 / page_size] : -1;
     };
-    int page_next = n_tiles > 0 ? page_of(0) : -1;
-    for (int t = 0; t < n_tiles; ++t) {
-      const int st = t & 1;
+    bool v_next = false;
+    int page_next = n_items > 0 ? page_of(tile_of(0, v_next)) : -1;
+    for (int i = 0; i < n_items; ++i) {
+      const int slot = i % RING;
       const int page = page_next;
-      if (t + 1 < n_tiles) page_next = page_of(t + 1);
+      const bool is_v = v_next;
+      if (i + 1 < n_items) page_next = page_of(tile_of(i + 1, v_next));
       bool ok = true;
-      if (t >= 2) ok = mbar_wait_bounded(kv_empty0 + 8 * st, ((t >> 1) - 1) & 1);
+      if (i >= RING) ok = mbar_wait_bounded(slot_empty0 + 8 * slot, ((i / RING) - 1) & 1);
       if (!__all_sync(0xffffffffu, ok)) {
         if (lane == 0) atomicExch(&failed, 1);
         break;
       }
       const int n_pages = __popc(__ballot_sync(0xffffffffu, page >= 0));
       if (lane == 0)
-        mbar_expect_tx(kv_full0 + 8 * st, (uint32_t)n_pages * 4u * page_size * 128u);
+        mbar_expect_tx(slot_full0 + 8 * slot, (uint32_t)n_pages * 2u * page_size * 128u);
       __syncwarp();
       if (page >= 0) {
-        const uint32_t dK = sK0 + st * TILE_BYTES, dV = sV0 + st * TILE_BYTES;
-        const int krow = ((page * 2) * n_kv_heads + kvh) * page_size;
-        const int vrow = krow + n_kv_heads * page_size;
-        const uint32_t off = lane * page_size * 128;
-        tma_load_2d(dK + off, &kv_map, kv_full0 + 8 * st, 0, krow);
-        tma_load_2d(dK + HALF_BYTES_TC + off, &kv_map, kv_full0 + 8 * st, 64, krow);
-        tma_load_2d(dV + off, &kv_map, kv_full0 + 8 * st, 0, vrow);
-        tma_load_2d(dV + HALF_BYTES_TC + off, &kv_map, kv_full0 + 8 * st, 64, vrow);
+        const uint32_t dst = ring + slot * TILE_BYTES + lane * page_size * 128;
+        const int r = ((page * 2 + (is_v ? 1 : 0)) * n_kv_heads + kvh) * page_size;
+        tma_load_2d(dst, &kv_map, slot_full0 + 8 * slot, 0, r);
+        tma_load_2d(dst + HALF_BYTES_TC, &kv_map, slot_full0 + 8 * slot, 64, r);
       }
     }
   } else if (warp == 1) {
@@ -197,9 +211,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
       bool ok = mbar_wait_bounded(q_full, 0);
       auto issue_s = [&](int t) {
         const int b = t & 1;
-        if (!mbar_wait_bounded(kv_full0 + 8 * b, (t >> 1) & 1)) return false;
+        const int item = k_item(t), slot = item % RING;
+        if (!mbar_wait_bounded(slot_full0 + 8 * slot, (item / RING) & 1)) return false;
         tmem_fence_after();
-        const uint32_t kbase = sK0 + b * TILE_BYTES;
+        const uint32_t kbase = ring + slot * TILE_BYTES;
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) {  // 16 columns of d per step; halves of 64 columns
           const uint32_t hoff = (k >> 2) * HALF_BYTES_TC + (k & 3) * 32;
@@ -207,21 +222,24 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                     k != 0 ? 1u : 0u);
         }
         umma_commit(s_full0 + 8 * b);
+        umma_commit(slot_empty0 + 8 * slot);
         return true;
       };
       auto issue_pv = [&](int t) {
         const int b = t & 1;
         if (!mbar_wait_bounded(p_full0 + 8 * b, (t >> 1) & 1)) return false;
         if (t >= 2 && !mbar_wait_bounded(o_empty0 + 8 * b, ((t >> 1) - 1) & 1)) return false;
+        const int item = v_item(t, n_tiles), slot = item % RING;
+        if (!mbar_wait_bounded(slot_full0 + 8 * slot, (item / RING) & 1)) return false;
         tmem_fence_after();
-        const uint32_t vbase = sV0 + b * TILE_BYTES;
+        const uint32_t vbase = ring + slot * TILE_BYTES;
 #pragma unroll
         for (int k = 0; k < TK / 16; ++k) {  // 16 keys per step: 8 columns of packed P, 2048 bytes of V
           umma_bf16_ts(tmem_base + 256 + b * 128, tmem_base + b * 128 + k * 8,
                        umma_desc_mn(vbase + k * 2048, HALF_BYTES_TC), idesc_o, k != 0 ? 1u : 0u);
         }
         umma_commit(o_full0 + 8 * b);
-        umma_commit(kv_empty0 + 8 * b);
+        umma_commit(slot_empty0 + 8 * slot);
         return true;
       };
       if (ok) ok = issue_s(0);
