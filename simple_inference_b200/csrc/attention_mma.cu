@@ -616,34 +616,42 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, const bf16*
   cp_async_wait<0>();
   __syncthreads();  // barriers initialised, stages zeroed, Q in place
 
-  // one lane issues the boxes of tile number `i` of this block into stage i % TMA_STAGES
+  // Warp 0 issues the boxes of tile number `i` of this block into stage i % TMA_STAGES: lane pg
+  // looks up and fetches page pg of the tile, so a tile's table reads are in flight together
+  // and the next tile's are under way while this one is computed.
   const int pages_per_tile = KV_TILE / page_size;
-  auto issue = [&](int i) {
+  auto lookup = [&](int i) {
+    if (i >= n_my || lane >= pages_per_tile) return -1;
+    const int j0 = (tile_a + i) * KV_TILE + lane * page_size;
+    return (j0 <= pos && j0 + page_size - 1 >= k_lo_all) ? table[j0 / page_size] : -1;
+  };
+  auto issue = [&](int i, int page) {
     const int st = i % TMA_STAGES;
-    const int key0 = (tile_a + i) * KV_TILE;
-    const uint32_t dst0 = stages0 + st * TMA_STAGE_BYTES;
-    int n_boxes = 0;
-    for (int pg = 0; pg < pages_per_tile; ++pg) {
-      const int j0 = key0 + pg * page_size;
-      if (j0 <= pos && j0 + page_size - 1 >= k_lo_all) ++n_boxes;
-    }
-    mbar_expect_tx(full0 + 8 * st, (uint32_t)n_boxes * 2u * HALVES * page_size * 128u);
-    for (int pg = 0; pg < pages_per_tile; ++pg) {
-      const int j0 = key0 + pg * page_size;
-      if (!(j0 <= pos && j0 + page_size - 1 >= k_lo_all)) continue;
-      const int page = table[j0 / page_size];
+    const uint32_t dst0 = stages0 + st * TMA_STAGE_BYTES + lane * page_size * 128;
+    const int n_boxes = __popc(__ballot_sync(0xffffffffu, page >= 0));
+    if (lane == 0)
+      mbar_expect_tx(full0 + 8 * st, (uint32_t)n_boxes * 2u * HALVES * page_size * 128u);
+    __syncwarp();
+    if (page >= 0) {
       const int krow = ((page * 2) * n_kv_heads + kvh) * page_size;
       const int vrow = krow + n_kv_heads * page_size;
 #pragma unroll
       for (int h = 0; h < HALVES; ++h) {
-        tma_load_2d(dst0 + h * HALF_BYTES + pg * page_size * 128, &pool_map, full0 + 8 * st, h * 64, krow);
-        tma_load_2d(dst0 + (HALVES + h) * HALF_BYTES + pg * page_size * 128, &pool_map,
-                    full0 + 8 * st, h * 64, vrow);
+        tma_load_2d(dst0 + h * HALF_BYTES, &pool_map, full0 + 8 * st, h * 64, krow);
+        tma_load_2d(dst0 + (HALVES + h) * HALF_BYTES, &pool_map, full0 + 8 * st, h * 64, vrow);
       }
     }
   };
-  if (tid == 0)
-    for (int i = 0; i < TMA_STAGES - 1 && i < n_my; ++i) issue(i);
+  int page_next = -1;
+  if (warp == 0) {
+    int first[TMA_STAGES];
+#pragma unroll
+    for (int i = 0; i < TMA_STAGES; ++i) first[i] = lookup(i);
+#pragma unroll
+    for (int i = 0; i < TMA_STAGES - 1; ++i)
+      if (i < n_my) issue(i, first[i]);
+    page_next = first[TMA_STAGES - 1];
+  }
 
   float o[D / 8][4];
 #pragma unroll
@@ -656,13 +664,15 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, const bf16*
   for (int i = 0; i < n_my && ok; ++i) {
     const int st = i % TMA_STAGES;
     const uint32_t use = (uint32_t)(i / TMA_STAGES);  // how often this stage was used before
-    if (tid == 0) {  // refill the stage that tile i-1 used, once all four warps have left it
+    if (warp == 0) {  // refill the stage that tile i-1 used, once all four warps have left it
       const int nx = i + TMA_STAGES - 1;
       if (nx < n_my) {
         const int nst = nx % TMA_STAGES;
         const uint32_t nuse = (uint32_t)(nx / TMA_STAGES);
-        if (nuse == 0 || mbar_wait_bounded(empty0 + 8 * nst, (nuse - 1) & 1u)) issue(nx);
-        else atomicExch(&failed, 1);
+        const bool free_now = nuse == 0 || mbar_wait_bounded(empty0 + 8 * nst, (nuse - 1) & 1u);
+        if (__all_sync(0xffffffffu, free_now)) issue(nx, page_next);
+        else if (lane == 0) atomicExch(&failed, 1);
+        page_next = lookup(nx + 1);
       }
     }
     __syncwarp();

@@ -14,6 +14,7 @@ float32 products run the hand-written FMA kernel, never a tensor-core mode.
 from __future__ import annotations
 
 import ctypes
+import functools
 
 import torch
 
@@ -321,25 +322,35 @@ def attention_generic(q: torch.Tensor, pool: torch.Tensor, block_table: torch.Te
 
 
 MAX_KV_SPLITS = 32
-_RESIDENT_BLOCKS = 3 * 148  # decode-attention blocks that fit on the GPU at once (3 per SM)
+# Cost model of the decode-attention kernel, fitted to timings on the 3B shape (24 query heads
+# in 8 groups, head size 128, 1 to 64 sequences, 512 to 8192 keys): a block costs a fixed
+# part plus a part per 64-key tile, the blocks run in waves of as many as fit on the GPU
+# (3 per SM), and joining the splits costs a little more with each split.
+_RESIDENT_BLOCKS = 3 * 148
+_BLOCK_US, _TILE_US, _MERGE_US, _MERGE_SPLIT_US = 4.0, 1.17, 2.0, 0.1
+
+
+@functools.lru_cache(maxsize=4096)
+def _plan_kv_splits(base: int, tiles: int) -> int:
+    best, best_t = 1, float("inf")
+    for s in range(1, min(MAX_KV_SPLITS, tiles) + 1):
+        per = -(-tiles // s)
+        waves = -(-base * s // _RESIDENT_BLOCKS)
+        t = waves * (_BLOCK_US + per * _TILE_US)
+        if s > 1:
+            t += _MERGE_US + s * _MERGE_SPLIT_US
+        if t < best_t - 1e-9:
+            best, best_t = s, t
+    return best
 
 
 def plan_kv_splits(n_single: int, num_q_heads: int, num_kv_heads: int, max_kv_len: int) -> int:
-    """How many blocks share the keys of one (sequence, kv head) in the decode kernel.
-
-    Measured on the 3B shape: a block works best on four to eight 64-key tiles; beyond
-    about 2,000 blocks more splits only add merge work; and when even that leaves the
-    SMs short of blocks (one or two sequences), one tile per block.
-    """
+    """How many blocks share the keys of one (sequence, kv head) in the decode kernel:
+    the number that the cost model above makes cheapest."""
     group = num_q_heads // num_kv_heads
     base = max(1, n_single * num_kv_heads * ((group + 15) // 16))
     tiles = max(1, (max_kv_len + 63) // 64)
-    splits = max(1, tiles // 4)
-    if base * splits > 2048:
-        splits = max(1, 2048 // base)
-    if base * splits < _RESIDENT_BLOCKS:
-        splits = min(tiles, (_RESIDENT_BLOCKS + base - 1) // base)
-    return max(1, min(MAX_KV_SPLITS, splits))
+    return _plan_kv_splits(base, tiles)
 
 
 def paged_attention(q: torch.Tensor, pool: torch.Tensor, ctx, group: int, out: torch.Tensor,
