@@ -15,12 +15,13 @@ from __future__ import annotations
 
 import ctypes
 import functools
+import os
 
 import torch
 
 from .build import KernelBuildError, load_library
 
-_CORE_SOURCES = ["rowwise.cu", "rope_kv.cu", "gemm_fp32.cu", "gemm_skinny.cu", "gemm_tc.cu",
+_CORE_SOURCES = ["rowwise.cu", "rope_kv.cu", "gemm_fp32.cu", "gemm_skinny.cu", "gemm_tc.cu", "gemm_tc2.cu",
                  "attention_generic.cu", "sampling.cu"]
 
 _ERRORS = {
@@ -197,17 +198,26 @@ def _tc_ok(x: torch.Tensor, weight: torch.Tensor, n_out: int) -> bool:
             and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
 
 
-def linear_tc(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, swiglu: bool = False) -> torch.Tensor:
-    """The tcgen05 product: ``out = x @ weight.T`` (bfloat16), or its SwiGLU form."""
+PAIRED_MIN_ROWS = 256  # from this many rows a tile of 256 rows on a pair of SMs is full
+
+
+def linear_tc(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, swiglu: bool = False,
+              paired: bool | None = None) -> torch.Tensor:
+    """The tcgen05 product: ``out = x @ weight.T`` (bfloat16), or its SwiGLU form.
+
+    ``paired``: run on pairs of SMs (256-row tiles); by default from 256 rows on."""
     _dev(x, weight, out)
     m, k = x.shape
     n = out.shape[1]
     if out.dtype != torch.bfloat16 or out.shape[0] != m or weight.shape != ((2 * n if swiglu else n), k) \
             or out.stride(0) % 8 != 0 or out.data_ptr() % 16 != 0:
         raise KernelError("linear_tc: operands do not fit")
-    _check(core().si_gemm_tc_bf16(_p(x), x.stride(0), _p(weight), _p(out), out.stride(0), m, n, k,
-                                  2 if swiglu else 0, _p(status_tensor(x.device)), _stream()),
-           "gemm_tc")
+    if paired is None:
+        paired = m >= PAIRED_MIN_ROWS and not os.environ.get("SI_B200_TC_UNPAIRED")
+    fn = core().si_gemm_tc2_bf16 if paired else core().si_gemm_tc_bf16
+    _check(fn(_p(x), x.stride(0), _p(weight), _p(out), out.stride(0), m, n, k,
+              2 if swiglu else 0, _p(status_tensor(x.device)), _stream()),
+           "gemm_tc2" if paired else "gemm_tc")
     return out
 
 

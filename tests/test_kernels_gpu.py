@@ -345,6 +345,31 @@ def test_weight_streaming_product_for_few_rows(ops, m, n, k):
     assert torch.equal(one[0], out32[m - 1])
 
 
+@pytest.mark.parametrize("m,n,k", [(256, 512, 64), (300, 264, 72), (257, 40, 8), (2048, 3072, 3072),
+                                   (700, 5120, 200)])
+def test_tensor_memory_product_on_sm_pairs(ops, m, n, k):
+    """The same product with 256-row tiles on clusters of two blocks (tcgen05 cta_group::2),
+    against float32 and against the one-block kernel; plain and SwiGLU; ragged edges."""
+    g = gen(9)
+    x = (torch.randn(m, k, device=dev(), generator=g) * 0.5).bfloat16()
+    w = (torch.randn(2 * n, k, device=dev(), generator=g) * 0.1).bfloat16()
+    ref = x.float() @ w.float().T
+    pair = torch.zeros(m, 2 * n, device=dev(), dtype=torch.bfloat16)
+    ops.linear_tc(x, w, pair, paired=True)
+    ops.check_status()
+    assert (pair.float() - ref).abs().max() < 8e-3 * max(1.0, float(ref.abs().max()))
+    single = torch.zeros(m, 2 * n, device=dev(), dtype=torch.bfloat16)
+    ops.linear_tc(x, w, single, paired=False)
+    ops.check_status()
+    assert torch.equal(pair, single), "both kernels add the k-steps in the same order"
+    fused = torch.zeros(m, n, device=dev(), dtype=torch.bfloat16)
+    ops.linear_tc(x, w, fused, swiglu=True, paired=True)
+    ops.check_status()
+    gate, up = ref[:, :n], ref[:, n:]
+    want = gate * torch.sigmoid(gate) * up
+    assert (fused.float() - want).abs().max() < 8e-3 * max(1.0, float(want.abs().max()))
+
+
 @pytest.mark.parametrize("m,n,k", [(128, 256, 64), (130, 264, 72), (96, 40, 8), (300, 5120, 3072),
                                    (2048, 3072, 8192), (1000, 331 * 8, 120)])
 def test_tensor_memory_product_for_many_rows(ops, m, n, k):
