@@ -175,8 +175,15 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
           const uint32_t a_src = base + s * T2_STAGE_BYTES;
           const uint64_t da = umma_desc(a_src), db = umma_desc(a_src + T2_A_BYTES);
 #pragma unroll
-          for (int k = 0; k < T2_BK / 16; ++k)
+          for (int k = 0; k < T2_BK / 16; ++k) {
+#ifdef SI_T2_TWO_CHAINS
+            // experiment: even and odd k-steps add into two accumulators, so that consecutive
+            // instructions do not depend on each other
+            umma_bf16_pair(d_tmem + (k & 1) * 128, da + 2 * k, db + 2 * k, idesc, (kb | (k >> 1)) != 0 ? 1u : 0u);
+#else
             umma_bf16_pair(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+#endif
+          }
           umma_commit_pair(empty0 + 8 * s);
         }
         if (ok) umma_commit_pair(acc_full0 + 8 * buf);
@@ -242,6 +249,24 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             }
           }
         }
+        if (TILE_N_OUT % 32 != 0) {  // a last half-width chunk of 16 columns
+          constexpr int c0 = TILE_N_OUT / 32 * 32;
+          uint32_t a[16];
+          tmem_ld16(taddr + c0, a);
+          tmem_ld_wait();
+          if (row < M) {
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+              const int col = n0 + c0 + j * 8;
+              if (col < n_out) {
+                float w8[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) w8[i] = __uint_as_float(a[j * 8 + i]);
+                store8<bf16>(orow + c0 + j * 8, w8);
+              }
+            }
+          }
+        }
       }
       tmem_fence_before();
       __syncwarp();
@@ -261,13 +286,15 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
   }
 }
 
-// Tile width on n_pairs persistent pairs: a multiple of 32 (each block holds half of the weight
-// rows, in whole 16-row steps) that spreads the tiles evenly and wastes little of the last tile.
+// Tile width on n_pairs persistent pairs: a multiple of 16 (each block holds half of the weight
+// rows, in whole 8-row swizzle groups) that spreads the tiles evenly and wastes little of the
+// last tile.  The time of a tile grows with its width, so a narrower tile that fills the last
+// round is better than a wide one that leaves pairs idle.
 static int choose_bn2(int M, int N, int n_pairs) {
   const int tiles_m = (M + 2 * T2_BM - 1) / (2 * T2_BM);
   int best = 256;
   double best_score = -1.0;
-  for (int bn = 256; bn >= 128; bn -= 32) {
+  for (int bn = 256; bn >= 128; bn -= 16) {
     const long long tiles = (long long)tiles_m * ((N + bn - 1) / bn);
     const long long per_pair = (tiles + n_pairs - 1) / n_pairs;
     const double balance = (double)tiles / ((double)per_pair * n_pairs);
@@ -343,18 +370,25 @@ SI_API int si_gemm_tc2_bf16(const void* X, int ldx, const void* W, void* out, in
     return launch_tc2<T2_EPI_SWIGLU, 256>(map_x, map_w, (bf16*)out, ldo, M, N, K, N, status, n_sms,
                                           stream);
   }
-  const int bn = choose_bn2(M, N, n_sms / 2);
+  int bn = choose_bn2(M, N, n_sms / 2);
+  if (const char* force = getenv("SI_B200_TC2_BN")) bn = atoi(force);  // a developer's knob for timing
   if (!make_bf16_map(&map_w, W, N, K, K, bn / 2)) return SI_ERR_UNSUPPORTED;
+#define SI_T2_CASE(W)                                                                          \
+  case W:                                                                                      \
+    return launch_tc2<T2_EPI_BF16, W>(map_x, map_w, (bf16*)out, ldo, M, N, K, 0, status, n_sms, \
+                                      stream)
   switch (bn) {
-    case 256:
-      return launch_tc2<T2_EPI_BF16, 256>(map_x, map_w, (bf16*)out, ldo, M, N, K, 0, status, n_sms, stream);
-    case 224:
-      return launch_tc2<T2_EPI_BF16, 224>(map_x, map_w, (bf16*)out, ldo, M, N, K, 0, status, n_sms, stream);
-    case 192:
-      return launch_tc2<T2_EPI_BF16, 192>(map_x, map_w, (bf16*)out, ldo, M, N, K, 0, status, n_sms, stream);
-    case 160:
-      return launch_tc2<T2_EPI_BF16, 160>(map_x, map_w, (bf16*)out, ldo, M, N, K, 0, status, n_sms, stream);
+    SI_T2_CASE(256);
+    SI_T2_CASE(240);
+    SI_T2_CASE(224);
+    SI_T2_CASE(208);
+    SI_T2_CASE(192);
+    SI_T2_CASE(176);
+    SI_T2_CASE(160);
+    SI_T2_CASE(144);
     default:
-      return launch_tc2<T2_EPI_BF16, 128>(map_x, map_w, (bf16*)out, ldo, M, N, K, 0, status, n_sms, stream);
+      return launch_tc2<T2_EPI_BF16, 128>(map_x, map_w, (bf16*)out, ldo, M, N, K, 0, status, n_sms,
+                                          stream);
   }
+#undef SI_T2_CASE
 }

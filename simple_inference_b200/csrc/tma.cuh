@@ -39,17 +39,26 @@ __device__ __forceinline__ unsigned long long global_ns() {
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
-// Bounded wait for the phase with the given parity; false after TMA_WAIT_LIMIT_NS.
+// Bounded wait for the phase with the given parity; false after TMA_WAIT_LIMIT_NS.  The clock
+// is read only once the barrier has been found closed a few times: reading %globaltimer costs
+// hundreds of cycles, which a wait that succeeds at once (the common case in a full pipeline)
+// must not pay.
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+  return done != 0;
+}
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity) {
+#pragma unroll 1
+  for (int i = 0; i < 16; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = global_ns();
   for (uint32_t spin = 0;; ++spin) {
-    uint32_t done;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(done) : "r"(bar), "r"(parity) : "memory");
-    if (done) return true;
+    if (mbar_try_wait(bar, parity)) return true;
     if ((spin & 63u) == 63u && global_ns() - t0 > TMA_WAIT_LIMIT_NS) return false;
   }
 }
