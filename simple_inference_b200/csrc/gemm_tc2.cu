@@ -175,15 +175,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
           const uint32_t a_src = base + s * T2_STAGE_BYTES;
           const uint64_t da = umma_desc(a_src), db = umma_desc(a_src + T2_A_BYTES);
 #pragma unroll
-          for (int k = 0; k < T2_BK / 16; ++k) {
-#ifdef SI_T2_TWO_CHAINS
-            // experiment: even and odd k-steps add into two accumulators, so that consecutive
-            // instructions do not depend on each other
-            umma_bf16_pair(d_tmem + (k & 1) * 128, da + 2 * k, db + 2 * k, idesc, (kb | (k >> 1)) != 0 ? 1u : 0u);
-#else
+          for (int k = 0; k < T2_BK / 16; ++k)
             umma_bf16_pair(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
-#endif
-          }
           umma_commit_pair(empty0 + 8 * s);
         }
         if (ok) umma_commit_pair(acc_full0 + 8 * buf);
@@ -370,8 +363,7 @@ SI_API int si_gemm_tc2_bf16(const void* X, int ldx, const void* W, void* out, in
     return launch_tc2<T2_EPI_SWIGLU, 256>(map_x, map_w, (bf16*)out, ldo, M, N, K, N, status, n_sms,
                                           stream);
   }
-  int bn = choose_bn2(M, N, n_sms / 2);
-  if (const char* force = getenv("SI_B200_TC2_BN")) bn = atoi(force);  // a developer's knob for timing
+  const int bn = choose_bn2(M, N, n_sms / 2);
   if (!make_bf16_map(&map_w, W, N, K, K, bn / 2)) return SI_ERR_UNSUPPORTED;
 #define SI_T2_CASE(W)                                                                          \
   case W:                                                                                      \
