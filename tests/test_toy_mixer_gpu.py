@@ -1,6 +1,8 @@
 """A mixer with state of its own, a position encoding of its own and an architecture of
 its own, all defined HERE, are registered, built, given random weights, and stepped in
-portions and mixed batches, without a change to any file of the framework.
+portions and mixed batches, without a change to any file of the framework.  Further down:
+a feed-forward that routes each token to one of several experts, a norm of another kind,
+and a run order that runs a layer twice.
 
 The toy mixer keeps a decaying sum per request: s <- decay * s + x_t, y_t = W s.  Its state
 is one row of fixed size per request (the cache manager's slots), so it must be carried
@@ -178,3 +180,186 @@ def test_toy_architecture_registers_builds_and_steps(tmp_path):
         feed(step)
     for i in range(3):
         assert (torch.cat(got[i]) - want[i]).abs().max() < 2e-5, f"sequence {i}"
+
+
+# --------------------------------------------------------------------------------------
+# A feed-forward with routing and a norm of another kind, again defined here.
+# --------------------------------------------------------------------------------------
+
+def define_routed():
+    from simple_inference_b200 import ops
+    from simple_inference_b200.config import register_architecture
+    from simple_inference_b200.config.model_config import LlamaConfig
+    from simple_inference_b200.models.llama import llama_layer_plan
+    from simple_inference_b200.models.plan import LayerPlan, ModelPlan, RunStep
+    from simple_inference_b200.parts import (FeedForward, Norm, PartSpec, TensorSpec,
+                                             register_feed_forward, register_norm)
+
+    @register_feed_forward("toy_top1_experts")
+    class Top1Experts(FeedForward):
+        """Every token goes to the one expert its router logit (float32) is largest for, and the
+        expert's output is scaled by the softmax weight of that logit: y = p_e W2_e relu(W1_e x)."""
+
+        def __init__(self, hidden_size: int, expert_size: int, num_experts: int):
+            self.h, self.f, self.e = hidden_size, expert_size, num_experts
+
+        def tensors(self):
+            t = {"router": TensorSpec((self.e, self.h))}
+            for e in range(self.e):
+                t[f"w1_{e}"] = TensorSpec((self.f, self.h))
+                t[f"w2_{e}"] = TensorSpec((self.h, self.f))
+            return t
+
+        def bind(self, tensors, rt):
+            super().bind(tensors, rt)
+            self.t = tensors
+
+        def forward(self, x, ctx):
+            n = x.shape[0]
+            logits = torch.empty(n, self.e, dtype=torch.float32, device=x.device)
+            ops.linear(x.float(), self.t["router"].float(), logits)       # router in float32
+            prob, choice = torch.softmax(logits, dim=-1).max(dim=-1)
+            out = ctx.ws.get("toy.experts", (n, self.h), x.dtype)
+            out.zero_()
+            for e in range(self.e):
+                rows = (choice == e).nonzero().flatten()
+                if rows.numel() == 0:
+                    continue
+                xe = x[rows].contiguous()
+                mid = torch.empty(rows.numel(), self.f, dtype=x.dtype, device=x.device)
+                ops.linear(xe, self.t[f"w1_{e}"], mid)
+                mid.relu_()
+                ye = torch.empty(rows.numel(), self.h, dtype=x.dtype, device=x.device)
+                ops.linear(mid, self.t[f"w2_{e}"], ye)
+                out[rows] = (ye.float() * prob[rows, None]).to(x.dtype)
+            return out
+
+    @register_norm("toy_centred")
+    class CentredNorm(Norm):
+        """Subtracts the mean, divides by the standard deviation, multiplies by a gain."""
+
+        def __init__(self, hidden_size: int, eps: float):
+            self.h, self.eps = hidden_size, eps
+
+        def tensors(self):
+            return {"weight": TensorSpec((self.h,), kind="vector", init="gain")}
+
+        def bind(self, tensors, rt):
+            super().bind(tensors, rt)
+            self.weight = tensors["weight"]
+
+        def forward(self, residual, ctx, tag="norm"):
+            return self.add_forward(residual, None, ctx, None, tag)
+
+        def add_forward(self, residual, delta, ctx, rows=None, tag="norm"):
+            if rows is None:
+                if delta is not None:
+                    residual.add_(delta.float())
+                x = residual
+            else:
+                x = residual[rows.long()]
+                if delta is not None:
+                    x = x + delta[rows.long()].float()
+            x = x - x.mean(-1, keepdim=True)
+            y = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + self.eps) * self.weight.float()
+            return y.to(self.rt.dtype)
+
+    @dataclass(kw_only=True)
+    class RoutedConfig(LlamaConfig):
+        num_experts: int = 3
+        expert_size: int = 40
+
+    def routed_plan(cfg: RoutedConfig) -> ModelPlan:
+        layers = []
+        norm = PartSpec("toy_centred", {"hidden_size": cfg.hidden_size, "eps": cfg.rms_norm_eps})
+        for i in range(cfg.num_hidden_layers):
+            lp = llama_layer_plan(cfg, i)
+            params = dict(lp.block.params)
+            names = dict(lp.tensor_names)
+            params["feed_forward_norm"] = norm
+            if i % 2 == 0:  # even layers: experts; odd layers keep the dense feed-forward
+                params["feed_forward"] = PartSpec("toy_top1_experts", {
+                    "hidden_size": cfg.hidden_size, "expert_size": cfg.expert_size,
+                    "num_experts": cfg.num_experts})
+                names = {k: v for k, v in names.items() if not k.startswith("feed_forward.")}
+                names["feed_forward.router"] = f"model.layers.{i}.moe.router"
+                for e in range(cfg.num_experts):
+                    names[f"feed_forward.w1_{e}"] = f"model.layers.{i}.moe.{e}.w1"
+                    names[f"feed_forward.w2_{e}"] = f"model.layers.{i}.moe.{e}.w2"
+            layers.append(LayerPlan(PartSpec("prenorm", params), names))
+        # the run order is data: layer 1 runs twice, its second run with a cache of its own
+        order = [RunStep(0, 0), RunStep(1, 1), RunStep(1, 2)]
+        return ModelPlan(
+            hidden_size=cfg.hidden_size, vocab_size=cfg.vocab_size, layers=layers, run_order=order,
+            final_norm=norm, tie_embeddings=cfg.tie_word_embeddings,
+            embedding_name="model.embed_tokens.weight",
+            final_norm_names={"weight": "model.norm.weight"}, head_name="lm_head.weight",
+            max_positions=cfg.max_position_embeddings)
+
+    register_architecture("RoutedToyForCausalLM", RoutedConfig, routed_plan)
+
+
+def plain_routed(cfg, w, ids):
+    from tests import plain_llama as pl
+    eps = cfg["rms_norm_eps"]
+
+    def centred(x, g):
+        x = x - x.mean(-1, keepdim=True)
+        return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * g
+
+    x = w["model.embed_tokens.weight"][torch.tensor(ids)]
+    pos = list(range(len(ids)))
+    freqs = pl.rope_frequencies(pl.head_dim_of(cfg), cfg["rope_theta"], None)
+    for i in (0, 1, 1):
+        p = f"model.layers.{i}."
+        h = pl.rmsnorm(x, w[p + "input_layernorm.weight"], eps)
+        x = x + pl.attention_layer(h, w, p + "self_attn.", cfg, pos, freqs)
+        h = centred(x, w[p + "post_attention_layernorm.weight"])
+        if i % 2 == 0:
+            prob, choice = torch.softmax(h @ w[p + "moe.router"].T, dim=-1).max(dim=-1)
+            y = torch.zeros_like(h)
+            for t in range(len(ids)):
+                e = int(choice[t])
+                y[t] = prob[t] * (w[f"{p}moe.{e}.w2"] @ torch.relu(w[f"{p}moe.{e}.w1"] @ h[t]))
+            x = x + y
+        else:
+            x = x + pl.mlp(h, w, p + "mlp.")
+    return centred(x, w["model.norm.weight"]) @ w["model.embed_tokens.weight"].T
+
+
+def test_routed_feed_forward_another_norm_and_a_layer_run_twice(tmp_path):
+    define_routed()
+    from simple_inference_b200 import load_model, write_random_model
+    from simple_inference_b200.cache import CacheManager
+    from simple_inference_b200.engine import ModelRunner, StepEntry
+    from tests import plain_llama
+    config = {
+        "architectures": ["RoutedToyForCausalLM"], "num_hidden_layers": 2, "hidden_size": 56,
+        "num_attention_heads": 2, "num_key_value_heads": 2, "head_dim": 32,
+        "intermediate_size": 88, "vocab_size": 77, "rope_theta": 5000.0, "rms_norm_eps": 1e-4,
+        "tie_word_embeddings": True, "max_position_embeddings": 128, "torch_dtype": "float32",
+        "num_experts": 3, "expert_size": 40,
+    }
+    write_random_model(tmp_path, config, seed=4)
+    cfg, model = load_model(tmp_path, "float32", DEV)
+    specs = model.cache_specs()
+    assert len(specs) == 3, "two layers, three runs, three caches"
+    cache = CacheManager(specs, 4, 40, 2, 64, torch.float32, DEV)
+    runner = ModelRunner(model, cache, model.rt, 64, 2, 128, max_logit_rows=64)
+    pcfg, w = plain_llama.read_folder(tmp_path)
+    seqs = [random_ids(n, 77, 40 + n) for n in (37, 21)]
+    want = [plain_routed(pcfg, w, s) for s in seqs]
+    got = {0: [], 1: []}
+    fed = {0: 0, 1: 0}
+    cache.admit(0, 37)
+    cache.admit(1, 21)
+    for step in ([(0, 16)], [(0, 1), (1, 9)], [(1, 2), (0, 20)], [(1, 10)]):
+        entries = [StepEntry(i, seqs[i][fed[i]:fed[i] + n], list(range(n))) for i, n in step]
+        out = runner.step(entries).clone().cpu()
+        o = 0
+        for i, n in step:
+            got[i].append(out[o:o + n])
+            o += n
+            fed[i] += n
+    for i in range(2):
+        assert (torch.cat(got[i]) - want[i]).abs().max() < 3e-5, f"sequence {i}"
