@@ -47,7 +47,16 @@ TINY_C = {
     "rms_norm_eps": 3e-6, "tie_word_embeddings": True, "max_position_embeddings": 512,
     "torch_dtype": "float32",
 }
-TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+# A fourth with the head size (128) and lengths that the tcgen05 attention and the paired
+# tcgen05 product take, so that the engine meets them and not only the kernel tests.
+TINY_D = {
+    "architectures": ["LlamaForCausalLM"],
+    "num_hidden_layers": 2, "hidden_size": 256, "num_attention_heads": 4,
+    "num_key_value_heads": 2, "head_dim": 128, "intermediate_size": 384, "vocab_size": 300,
+    "rope_theta": 100000.0, "rope_scaling": None, "rms_norm_eps": 2e-5,
+    "tie_word_embeddings": False, "max_position_embeddings": 1024, "torch_dtype": "bfloat16",
+}
+TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
 
 
 @pytest.fixture(scope="session")

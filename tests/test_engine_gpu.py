@@ -45,7 +45,7 @@ def test_greedy_float32_equals_plain_in_every_regime(name, model_folders):
         assert list(alone.generate(p, 16)) == g
 
 
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "D"])
 def test_greedy_bfloat16_graphs_on_and_off_agree_with_plain(name, model_folders):
     cfg, w = plain_llama.read_folder(model_folders[name])
     prompts = [random_ids(n, cfg["vocab_size"], 80 + n) for n in (5, 17, 32, 3)]
