@@ -6,23 +6,26 @@
 // One block per (128-query tile of a sequence, query head); keys in tiles of 128.  Roles:
 //   warp 0             TMA producer: the Q tile once (two 64-column halves, straight from
 //                      the qkv buffer), then per key tile the K and V rows of its pages
-//                      (cp.async.bulk.tensor boxes of page_size x 64, 128-byte swizzle; one
-//                      lane per page) into a ring of slots that K and V tiles share, in the
+//                      (one cp.async.bulk.tensor box per page: all its rows, both column
+//                      halves, 128-byte swizzle; one lane per page) into a ring of slots that K and V tiles share, in the
 //                      order the products need them; mbarriers count the bytes.
 //   warp 1, one lane   MMA issuer: S = Q K^T (M128 N128, eight K16 steps; Q and K are
 //                      K-major) into one of two S buffers in tensor memory, and
 //                      PV = P V (P is read from tensor memory, where the softmax warps put it
 //                      over the S it came from; V is MN-major: its rows are keys) into one
-//                      of two output buffers.  S of the next tile is issued
-//                      before PV of this one, so the tensor core works while softmax runs.
-//   warps 2..9         softmax, two threads per query row (64 keys and 64 output columns
-//                      each): read S with tcgen05.ld, trade the row maximum through shared
-//                      memory, mask edge tiles by absolute position, online softmax in
-//                      float32 (kernels/attention_kernel.py:231-241), round P to bfloat16
-//                      (:240) and store it to tensor memory as the next product's A operand;
-//                      read each tile's PV from tensor memory and keep O = O*alpha + PV in
-//                      registers (two-wide float32 instructions);
-//                      at the end divide by l and store.
+//                      of two output buffers (tiles of equal parity add up in the same one).
+//                      S of the next tile is issued before PV of this one, so the tensor
+//                      core works while softmax runs.
+//   warps 2..9         softmax, in two sets of four warps, one thread per query row.  Set b
+//                      owns tiles b, b+2, ...: it reads S with tcgen05.ld (once for the row
+//                      maximum, once for P), masks edge tiles by absolute position, runs the
+//                      online softmax in float32 (kernels/attention_kernel.py:231-241) with
+//                      two-wide fma and ex2.approx, rounds P to bfloat16 (:240) and stores it
+//                      to tensor memory as the next product's A operand.  The set's output
+//                      adds up in tensor memory (the products accumulate); it is rescaled
+//                      only when a row's maximum has grown by more than 2^8, every term of a
+//                      row staying relative to one maximum.  At the end the two sets' (m, l,
+//                      O) are joined like the parts of a split, divided by l and stored.
 // Every mbarrier wait is bounded; a block whose wait runs out writes NaN to its outputs.
 #include "tcgen05.cuh"
 
@@ -63,21 +66,6 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// O = O * alpha + PV for this thread's 64 output columns of buffer `o_addr`
-__device__ __forceinline__ void fold_pv(float2 (&o)[32], float alpha, uint32_t o_addr) {
-  uint32_t r0[32], r1[32];
-  tmem_ld32(o_addr, r0);
-  tmem_ld32(o_addr + 32, r1);
-  tmem_ld_wait();
-  const float2 a2 = make_float2(alpha, alpha);
-#pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    o[i] = __ffma2_rn(o[i], a2, make_float2(__uint_as_float(r0[2 * i]), __uint_as_float(r0[2 * i + 1])));
-    o[16 + i] = __ffma2_rn(o[16 + i], a2,
-                           make_float2(__uint_as_float(r1[2 * i]), __uint_as_float(r1[2 * i + 1])));
-  }
-}
-
 __global__ void __launch_bounds__(ATC_THREADS, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
                        const __grid_constant__ CUtensorMap kv_map,
@@ -94,7 +82,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
   const uint32_t bars = base + (1 + RING) * TILE_BYTES;
   // barriers, 8 bytes each
   const uint32_t q_full = bars, s_full0 = bars + 8, p_full0 = bars + 24, o_full0 = bars + 40,
-                 o_empty0 = bars + 56, tmem_slot = bars + 72, slot_full0 = bars + 80,
+                 tmem_slot = bars + 72, slot_full0 = bars + 80,
                  slot_empty0 = slot_full0 + 8 * RING;
   volatile uint32_t* tmem_slot_ptr =
       reinterpret_cast<volatile uint32_t*>(base_ptr + (1 + RING) * TILE_BYTES + 72);
@@ -113,9 +101,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
     }
     for (int i = 0; i < 2; ++i) {
       mbar_init(s_full0 + 8 * i, 1);
-      mbar_init(p_full0 + 8 * i, 8);
+      mbar_init(p_full0 + 8 * i, 4);   // the four warps of the set that owns the buffer
       mbar_init(o_full0 + 8 * i, 1);
-      mbar_init(o_empty0 + 8 * i, 8);
     }
     mbar_init_fence();
   }
@@ -192,13 +179,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
       }
       const int n_pages = __popc(__ballot_sync(0xffffffffu, page >= 0));
       if (lane == 0)
-        mbar_expect_tx(slot_full0 + 8 * slot, (uint32_t)n_pages * 2u * page_size * 128u);
+        mbar_expect_tx(slot_full0 + 8 * slot, (uint32_t)n_pages * page_size * 256u);
       __syncwarp();
       if (page >= 0) {
-        const uint32_t dst = ring + slot * TILE_BYTES + lane * page_size * 128;
-        const int r = ((page * 2 + (is_v ? 1 : 0)) * n_kv_heads + kvh) * page_size;
-        tma_load_2d(dst, &kv_map, slot_full0 + 8 * slot, 0, r);
-        tma_load_2d(dst + HALF_BYTES_TC, &kv_map, slot_full0 + 8 * slot, 64, r);
+        // the page's rows of this kv head, both column halves, in one copy (see make_page_map);
+        // in the slot, page i of the tile is page_size * 256 bytes from page i - 1
+        const uint32_t dst = ring + slot * TILE_BYTES + lane * page_size * 256;
+        const int group0 = ((page * 2) * n_kv_heads + kvh) * (page_size >> 3);
+        tma_load_5d(dst, &kv_map, slot_full0 + 8 * slot, 0, 0, 0, group0, is_v ? 1 : 0);
       }
     }
   } else if (warp == 1) {
@@ -217,8 +205,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
         const uint32_t kbase = ring + slot * TILE_BYTES;
 #pragma unroll
         for (int k = 0; k < HD / 16; ++k) {  // 16 columns of d per step; halves of 64 columns
-          const uint32_t hoff = (k >> 2) * HALF_BYTES_TC + (k & 3) * 32;
-          umma_bf16(tmem_base + b * 128, umma_desc(sQ + hoff), umma_desc(kbase + hoff), idesc_s,
+          // Q: two half tiles of 128 rows; K: the halves of every 8-row group side by side
+          const uint32_t q_off = (k >> 2) * HALF_BYTES_TC + (k & 3) * 32;
+          const uint32_t k_off = (k >> 2) * 1024 + (k & 3) * 32;
+          umma_bf16(tmem_base + b * 128, umma_desc(sQ + q_off), umma_desc(kbase + k_off, 2048), idesc_s,
                     k != 0 ? 1u : 0u);
         }
         umma_commit(s_full0 + 8 * b);
@@ -228,15 +218,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
       auto issue_pv = [&](int t) {
         const int b = t & 1;
         if (!mbar_wait_bounded(p_full0 + 8 * b, (t >> 1) & 1)) return false;
-        if (t >= 2 && !mbar_wait_bounded(o_empty0 + 8 * b, ((t >> 1) - 1) & 1)) return false;
         const int item = v_item(t, n_tiles), slot = item % RING;
         if (!mbar_wait_bounded(slot_full0 + 8 * slot, (item / RING) & 1)) return false;
         tmem_fence_after();
         const uint32_t vbase = ring + slot * TILE_BYTES;
 #pragma unroll
-        for (int k = 0; k < TK / 16; ++k) {  // 16 keys per step: 8 columns of packed P, 2048 bytes of V
+        for (int k = 0; k < TK / 16; ++k) {  // 16 keys per step: 8 columns of packed P, two 8-row groups of V
+          // the set's output adds up over its tiles (tiles b, b + 2, ...): only its first starts anew
+          // V: 16 keys are two 8-row groups 2048 bytes apart; the second column half 1024 bytes on
           umma_bf16_ts(tmem_base + 256 + b * 128, tmem_base + b * 128 + k * 8,
-                       umma_desc_mn(vbase + k * 2048, HALF_BYTES_TC), idesc_o, k != 0 ? 1u : 0u);
+                       umma_desc_mn(vbase + k * 4096, 1024, 2048), idesc_o, (t >= 2 || k != 0) ? 1u : 0u);
         }
         umma_commit(o_full0 + 8 * b);
         umma_commit(slot_empty0 + 8 * slot);
@@ -250,105 +241,164 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
       if (!ok) atomicExch(&failed, 1);
     }
   } else {  // ------------------------------------------------------- softmax and epilogue
-    // Two threads per query row: `part` 0 takes keys 0..63 of a tile and output columns
-    // 0..63, `part` 1 the rest; a warp reads the quarter of tensor memory its index allows.
+    // Two sets of four warps; set b owns the tiles b, b + 2, ... (S buffer b, output buffer b)
+    // and runs its own online softmax over them, one thread per query row, so the sets work
+    // out of step and neither waits for the other until the end, where their (m, l, O) join
+    // like the parts of a split.  A set's output stays in tensor memory and adds up there;
+    // it is rescaled only when a row's maximum grows by more than 2^RESCALE_AT (the sums
+    // stay exact: every term of a row is relative to the same stale maximum).
+    constexpr float RESCALE_AT = 8.0f;
     const int quarter = warp & 3;
-    const int part = (warp - 2) >> 2;
+    const int set = (warp - 2) >> 2;
     const int row = quarter * 32 + lane;
     const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
     const int my_pos = pos0 + row;
     const bool row_ok = row < n_rows;
-    float2 o[32];
-#pragma unroll
-    for (int i = 0; i < 32; ++i) o[i] = make_float2(0.0f, 0.0f);
-    float m_run = -INFINITY, l_run = 0.0f, alpha_prev = 0.0f;
+    const uint32_t s_addr = tmem_base + set * 128 + lane_off;        // S of the set's tiles, then P over it
+    const uint32_t o_addr = tmem_base + 256 + set * 128 + lane_off;  // the set's output
+    float m_run = -INFINITY, l_run = 0.0f;
     bool ok = true;
 
-    for (int t = 0; t < n_tiles; ++t) {  // no early exit: every thread meets every bar.sync
-      const int b = t & 1;
-      const int key0 = (tile_first + t) * TK + part * 64;
+    for (int t = set, j = 0; t < n_tiles; t += 2, ++j) {  // j: number of the tile within the set
+      const int key0 = (tile_first + t) * TK;
       // interior tiles need no mask: every key is at or before every row and inside the window
-      const bool need_mask = (tile_first + t) * TK + TK - 1 > pos0 ||
-                             (window > 0 && (tile_first + t) * TK <= k_hi - window);
-      if (ok && !mbar_wait_bounded(s_full0 + 8 * b, (t >> 1) & 1)) ok = false;
+      const bool need_mask = key0 + TK - 1 > pos0 || (window > 0 && key0 <= k_hi - window);
+      if (ok && !mbar_wait_bounded(s_full0 + 8 * set, j & 1)) ok = false;
       tmem_fence_after();
-      uint32_t s0[32], s1[32];
-      const uint32_t s_addr = tmem_base + b * 128 + part * 64 + lane_off;
-      tmem_ld32(s_addr, s0);
-      tmem_ld32(s_addr + 32, s1);
-      tmem_ld_wait();
-      if (need_mask) {
+      auto visible = [&](int key) {
+        return row_ok && key <= my_pos && (window <= 0 || key > my_pos - window);
+      };
+      // pass 1: the row's maximum over the tile.  The chunks are read last to first, each load
+      // under way while the chunk before it is worked on, and chunk 0 stays in registers for pass 2.
+      uint32_t ra[32], rb[32];
+      auto mask_chunk = [&](uint32_t (&r)[32], int c) {
+        if (need_mask) {
 #pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int j0 = key0 + i, j1 = key0 + 32 + i;
-          if (!(row_ok && j0 <= my_pos && (window <= 0 || j0 > my_pos - window))) s0[i] = 0xff800000u;
-          if (!(row_ok && j1 <= my_pos && (window <= 0 || j1 > my_pos - window))) s1[i] = 0xff800000u;
+          for (int i = 0; i < 32; ++i)
+            if (!visible(key0 + c * 32 + i)) r[i] = 0xff800000u;  // -inf: never the maximum, exp2 gives 0
+        }
+      };
+      auto max_chunk = [&](const uint32_t (&r)[32]) {
+        float a = fmaxf(__uint_as_float(r[0]), __uint_as_float(r[1]));
+#pragma unroll
+        for (int i = 2; i < 32; i += 2) a = fmax3(a, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+        return a;
+      };
+      tmem_ld32(s_addr + 96, ra);
+      tmem_ld_wait();
+      tmem_ld32(s_addr + 64, rb);
+      mask_chunk(ra, 3);
+      float mx = max_chunk(ra);
+      tmem_ld_wait();
+      tmem_ld32(s_addr + 32, ra);
+      mask_chunk(rb, 2);
+      mx = fmaxf(mx, max_chunk(rb));
+      tmem_ld_wait();
+      tmem_ld32(s_addr, rb);
+      mask_chunk(ra, 1);
+      mx = fmaxf(mx, max_chunk(ra));
+      tmem_ld_wait();
+      mask_chunk(rb, 0);
+      mx = fmaxf(mx, max_chunk(rb));
+      const float m_new = fmaxf(m_run, mx * scale_log2);
+      if (j == 0) {
+        m_run = m_new;  // nothing added up yet
+      } else {
+        const bool grow = m_new > m_run + RESCALE_AT || (m_run == -INFINITY && m_new != -INFINITY);
+        if (__any_sync(0xffffffffu, grow)) {
+          // the set's previous product must have landed before its output is touched
+          if (ok && !mbar_wait_bounded(o_full0 + 8 * set, (j - 1) & 1)) ok = false;
+          tmem_fence_after();
+          const float m_to = grow ? m_new : m_run;
+          const float alpha = (m_to == -INFINITY) ? 1.0f : ex2_approx(m_run - m_to);
+#pragma unroll 1
+          for (int c = 0; c < HD / 32; ++c) {
+            uint32_t r[32];
+            tmem_ld32(o_addr + c * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+            tmem_st32(o_addr + c * 32, r);
+          }
+          tmem_st_wait();
+          l_run *= alpha;
+          m_run = m_to;
         }
       }
-      float mx = fmaxf(__uint_as_float(s0[0]), __uint_as_float(s1[0]));
-#pragma unroll
-      for (int i = 1; i < 32; ++i) mx = fmax3(mx, __uint_as_float(s0[i]), __uint_as_float(s1[i]));
-      xmax[b][part][row] = mx;
-      asm volatile("bar.sync 1, 256;" ::: "memory");  // also: both parts hold their S in registers
-      mx = fmaxf(mx, xmax[b][part ^ 1][row]);
-      const float m_new = fmaxf(m_run, mx * scale_log2);
-      const float m_use = (m_new == -INFINITY) ? 0.0f : m_new;
-      const float alpha = ex2_approx(m_run - m_use);
-      // P = exp2(S * scale - m): masked entries are -inf and give 0
+      const float m_use = (m_run == -INFINITY) ? 0.0f : m_run;
+      // pass 2: P = exp2(S * scale - m), rounded to bfloat16, over the S it came from; chunk 0
+      // is still in registers, and each further chunk is loaded while the one before is worked on
       const float2 sc2 = make_float2(scale_log2, scale_log2), nm2 = make_float2(-m_use, -m_use);
       float2 acc = make_float2(0.0f, 0.0f);
-      uint32_t pk[32];
+      auto p_chunk = [&](const uint32_t (&r)[32], int c) {
+        uint32_t pk[16];
 #pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        float2 x = __ffma2_rn(make_float2(__uint_as_float(s0[2 * i]), __uint_as_float(s0[2 * i + 1])), sc2, nm2);
-        float2 y = __ffma2_rn(make_float2(__uint_as_float(s1[2 * i]), __uint_as_float(s1[2 * i + 1])), sc2, nm2);
-        x.x = ex2_approx(x.x); x.y = ex2_approx(x.y);
-        y.x = ex2_approx(y.x); y.y = ex2_approx(y.y);
-        acc = __fadd2_rn(acc, __fadd2_rn(x, y));
-        pk[i] = pack_bf16(x.x, x.y);
-        pk[16 + i] = pack_bf16(y.x, y.y);
-      }
-      tmem_st32(tmem_base + b * 128 + part * 32 + lane_off, pk);
+        for (int i = 0; i < 16; ++i) {
+          float2 x = __ffma2_rn(make_float2(__uint_as_float(r[2 * i]), __uint_as_float(r[2 * i + 1])), sc2, nm2);
+          x.x = ex2_approx(x.x);
+          x.y = ex2_approx(x.y);
+          acc = __fadd2_rn(acc, x);
+          pk[i] = pack_bf16(x.x, x.y);
+        }
+        tmem_st16(s_addr + c * 16, pk);  // 32 keys = 16 packed columns; behind the columns read so far
+      };
+      tmem_ld32(s_addr + 32, ra);
+      p_chunk(rb, 0);
+      tmem_ld_wait();
+      tmem_ld32(s_addr + 64, rb);
+      mask_chunk(ra, 1);
+      p_chunk(ra, 1);
+      tmem_ld_wait();
+      tmem_ld32(s_addr + 96, ra);
+      mask_chunk(rb, 2);
+      p_chunk(rb, 2);
+      tmem_ld_wait();
+      mask_chunk(ra, 3);
+      p_chunk(ra, 3);
       tmem_st_wait();
       tmem_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(p_full0 + 8 * b);
-      // fold in the previous tile's PV, which is relative to the previous maximum
-      if (t >= 1) {
-        const int pb = (t - 1) & 1;
-        if (ok && !mbar_wait_bounded(o_full0 + 8 * pb, ((t - 1) >> 1) & 1)) ok = false;
-        tmem_fence_after();
-        fold_pv(o, alpha_prev, tmem_base + 256 + pb * 128 + part * 64 + lane_off);
-        tmem_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(o_empty0 + 8 * pb);
-      }
-      alpha_prev = alpha;
-      l_run = l_run * alpha + (acc.x + acc.y);
-      m_run = m_new;
+      if (lane == 0) mbar_arrive(p_full0 + 8 * set);
+      l_run += acc.x + acc.y;
     }
-    if (n_tiles > 0) {  // the last tile's PV
-      const int pb = (n_tiles - 1) & 1;
-      if (ok && !mbar_wait_bounded(o_full0 + 8 * pb, ((n_tiles - 1) >> 1) & 1)) ok = false;
-      tmem_fence_after();
-      fold_pv(o, alpha_prev, tmem_base + 256 + pb * 128 + part * 64 + lane_off);
-    }
+
+    // ---- join the two sets: thread (set, row) writes output columns [64 set, 64 set + 64)
+    xmax[0][set][row] = m_run;
+    xsum[set][row] = l_run;
+    const int n_mine[2] = {(n_tiles + 1) / 2, n_tiles / 2};
+    for (int b = 0; b < 2; ++b)  // both sets' last products
+      if (ok && n_mine[b] > 0 && !mbar_wait_bounded(o_full0 + 8 * b, (n_mine[b] - 1) & 1)) ok = false;
+    tmem_fence_after();
     if (!ok) atomicExch(&failed, 1);
-    // the row's sum is the sum of its two threads' sums (the same maxima went into both)
-    xsum[part][row] = ok ? l_run : __int_as_float(0x7fc00000);
-    asm volatile("bar.sync 2, 256;" ::: "memory");
-    if (row_ok) {
-      const float inv = 1.0f / (xsum[0][row] + xsum[1][row]);
-      bf16* dst = out + (long long)(tok0 + row) * out_stride + (long long)h * HD + part * 64;
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    {
+      // (tcgen05.ld is a warp-wide instruction: every lane runs the loads, rows past the tile's
+      // end only skip the stores)
+      const float m0 = xmax[0][0][row], m1 = xmax[0][1][row];
+      const float mm = fmaxf(m0, m1);
+      const bool two = n_mine[1] > 0;  // the same for the whole block
+      const float w0 = (m0 == -INFINITY) ? 0.0f : ex2_approx(m0 - mm);
+      const float w1 = (!two || m1 == -INFINITY) ? 0.0f : ex2_approx(m1 - mm);
+      float inv = 1.0f / (xsum[0][row] * w0 + xsum[1][row] * w1);
+      if (!ok) inv = __int_as_float(0x7fc00000);
+      bf16* dst = out + (long long)(tok0 + row) * out_stride + (long long)h * HD + set * 64;
+#pragma unroll 1
+      for (int c = 0; c < 2; ++c) {
+        uint32_t r0[32], r1[32];
+        tmem_ld32(tmem_base + 256 + lane_off + set * 64 + c * 32, r0);
+        if (two) tmem_ld32(tmem_base + 384 + lane_off + set * 64 + c * 32, r1);
+        tmem_ld_wait();
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        float w8[8];
+        for (int q8 = 0; q8 < 4; ++q8) {
+          float w8[8];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          w8[2 * i] = o[c * 4 + i].x * inv;
-          w8[2 * i + 1] = o[c * 4 + i].y * inv;
+          for (int i = 0; i < 8; ++i) {
+            float v = __uint_as_float(r0[q8 * 8 + i]) * w0;
+            if (two && w1 != 0.0f) v += __uint_as_float(r1[q8 * 8 + i]) * w1;
+            w8[i] = v * inv;
+          }
+          if (row_ok) store8<bf16>(dst + c * 32 + q8 * 8, w8);
         }
-        store8<bf16>(dst + c * 8, w8);
       }
     }
   }
@@ -388,8 +438,7 @@ SI_API int si_attn_prefill_tc(const void* q, int q_stride, int n_tokens, const v
   if (n_tiles == 0) return SI_OK;
   CUtensorMap q_map, kv_map;
   if (!make_bf16_map(&q_map, q, n_tokens, n_q_heads * HD, q_stride, TQ)) return SI_ERR_UNSUPPORTED;
-  if (!make_bf16_map(&kv_map, pool, (long long)n_pages * 2 * n_kv_heads * page_size, HD, HD, page_size))
-    return SI_ERR_UNSUPPORTED;
+  if (!make_page_map(&kv_map, pool, n_pages, n_kv_heads, page_size, HD, 1)) return SI_ERR_UNSUPPORTED;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel,

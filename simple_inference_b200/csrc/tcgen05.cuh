@@ -10,10 +10,11 @@ namespace si {
 
 // Shared-memory operand descriptor: K-major rows of 128 bytes, 128-byte swizzle, groups of
 // 8 rows 1024 bytes apart (what a TMA box of 64 bfloat16 columns with SWIZZLE_128B writes).
-__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+// group_bytes: distance between consecutive 8-row groups (1024 when the tile is one block of rows).
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t group_bytes = 1024) {
   uint64_t d = (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
   d |= (uint64_t)1 << 16;            // leading byte offset (unused with a swizzle): 16 B
-  d |= (uint64_t)(1024 >> 4) << 32;  // stride byte offset between 8-row groups
+  d |= (uint64_t)((group_bytes >> 4) & 0x3FFFu) << 32;  // stride byte offset between 8-row groups
   d |= (uint64_t)1 << 46;            // descriptor version of this architecture
   d |= (uint64_t)2 << 61;            // SWIZZLE_128B
   return d;
@@ -26,10 +27,11 @@ __host__ __device__ constexpr uint32_t umma_idesc(int m, int n, bool b_mn_major 
 // Descriptor of an MN-major operand (for B: rows are k, each row holds 64 consecutive n in
 // 128 bytes, 128-byte swizzle): 8-row groups 1024 bytes apart along k, blocks of 64 n
 // `n_block_bytes` apart.
-__device__ __forceinline__ uint64_t umma_desc_mn(uint32_t smem_addr, uint32_t n_block_bytes) {
+__device__ __forceinline__ uint64_t umma_desc_mn(uint32_t smem_addr, uint32_t n_block_bytes,
+                                                 uint32_t k_group_bytes = 1024) {
   uint64_t d = (uint64_t)((smem_addr & 0x3FFFFu) >> 4);
   d |= (uint64_t)((n_block_bytes >> 4) & 0x3FFFu) << 16;  // leading byte offset: next 64 n
-  d |= (uint64_t)(1024 >> 4) << 32;                       // stride byte offset: next 8 k
+  d |= (uint64_t)((k_group_bytes >> 4) & 0x3FFFu) << 32;  // stride byte offset: next 8 k
   d |= (uint64_t)1 << 46;
   d |= (uint64_t)2 << 61;
   return d;
@@ -92,6 +94,15 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
         "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]),
         "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]),
         "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0],"
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]),
+        "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]),
+        "r"(r[14]), "r"(r[15])
       : "memory");
 }
 __device__ __forceinline__ void tmem_st_wait() {

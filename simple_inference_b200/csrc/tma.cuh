@@ -70,6 +70,14 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       " [%0], [%1, {%3, %4}], [%2];"
       ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
 }
+// five coordinates, innermost first (the innermost one's byte offset a multiple of 16)
+__device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int c0, int c1, int c2, int c3, int c4) {
+  asm volatile(
+      "cp.async.bulk.tensor.5d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4) : "memory");
+}
 // orders earlier generic-proxy writes to shared memory before later async-proxy (TMA) writes
 __device__ __forceinline__ void fence_proxy_async_smem() {
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -132,6 +140,47 @@ static inline bool make_bf16_map(CUtensorMap* map, const void* ptr, long long ro
   if (fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return false;
+  if (maps.size() > 4096) maps.clear();
+  maps.emplace(key, *map);
+  return true;
+}
+
+// Map of a paged key/value pool [pages, 2, kv_heads, page_size, head_dim] (bfloat16, head_dim a
+// multiple of 64, page_size a multiple of 8) that fetches a whole page of one kv head with ONE
+// copy.  Its five dimensions are: 64 columns of a row; the 8 rows of a group; the head_dim/64
+// column halves of a row; the 8-row groups of the pool, counted through all pages and heads;
+// keys or values.  A box of (64, 8, halves, page_size/8, kv) lands in shared memory as
+// [kv][group][half][8 rows x 128 bytes, swizzled]: for every column half the 8-row groups are
+// halves * 1024 bytes apart, which both ldmatrix and the tcgen05 operand descriptors take.
+// A copy costs the TMA unit about as much whatever its size, so a page in one copy instead of
+// one per half and per K/V is what lets small pages stream at full rate.
+// kv_in_box: 2 = keys and values of the page in one box (values behind keys), 1 = one of them
+// per box (coordinate 4 chooses).  The row coordinate (3) of page p, head h is
+// ((2 p) * kv_heads + h) * page_size / 8.
+static inline bool make_page_map(CUtensorMap* map, const void* pool, long long n_pages, int n_kv_heads,
+                                 int page_size, int head_dim, int kv_in_box) {
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> maps;
+  static std::mutex mutex;
+  const MapKey key{pool, n_pages, n_kv_heads, page_size * 1024 + head_dim, kv_in_box};
+  std::lock_guard<std::mutex> lock(mutex);
+  auto it = maps.find(key);
+  if (it != maps.end()) {
+    *map = it->second;
+    return true;
+  }
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (!fn || head_dim % 64 != 0 || page_size % 8 != 0 || n_pages <= 0) return false;
+  const cuuint64_t row_bytes = (cuuint64_t)head_dim * 2;
+  const cuuint64_t kv_rows = (cuuint64_t)n_kv_heads * page_size;  // from a key row to its value row
+  const cuuint64_t groups = (cuuint64_t)n_pages * 2 * kv_rows / 8;
+  cuuint64_t dims[5] = {64, 8, (cuuint64_t)head_dim / 64, groups - kv_rows / 8, 2};
+  cuuint64_t strides[4] = {row_bytes, 128, 8 * row_bytes, kv_rows * row_bytes};
+  cuuint32_t box[5] = {64, 8, (cuuint32_t)head_dim / 64, (cuuint32_t)page_size / 8, (cuuint32_t)kv_in_box};
+  cuuint32_t elem[5] = {1, 1, 1, 1, 1};
+  if (fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, const_cast<void*>(pool), dims, strides, box, elem,
+         CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+         CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
     return false;
   if (maps.size() > 4096) maps.clear();
   maps.emplace(key, *map);
