@@ -489,34 +489,26 @@ attn_decode_kernel(const bf16* __restrict__ q, int q_stride, const bf16* __restr
 
 // ------------------------------------------------------- decode, keys by TMA
 // The same kernel with keys and values brought in by the tensor memory accelerator
-// (head sizes that are multiples of 64, page sizes 8, 16, 32 or 64).  The keys and values
-// of one page and kv head arrive as ONE cp.async.bulk.tensor box (a 5-D map of the pool, see
-// make_page_map in tma.cuh: a copy costs the TMA unit about the same whatever it carries, so
-// 8 KB a copy instead of 2 KB is worth a third of the kernel's time); lane i of warp 0 looks up
-// and fetches page i of a tile, and an mbarrier with the expected byte count tells the four
-// warps when a 64-key stage is complete.  The warps hand a stage back through a second
-// mbarrier, so there is no block-wide barrier in the loop and nobody spends instructions on
-// copy addresses.  ldmatrix applies the swizzle (16-byte chunk c of a row lives at chunk
-// c ^ (row & 7) of its 128 bytes).
+// (head sizes that are multiples of 64, page sizes 8, 16, 32 or 64).  The pool of one layer
+// is a 2-D tensor [pages*2*kv_heads*page_size rows, D columns]; the keys (or values) of
+// one page and kv head are page_size consecutive rows, so one lane issues, per page and
+// 64-column half, one cp.async.bulk.tensor box with the 128-byte swizzle, and an mbarrier
+// with the expected byte count tells the four warps when a 64-key stage is complete.  The
+// warps hand a stage back through a second mbarrier, so there is no block-wide barrier in
+// the loop and nobody spends instructions on addresses.  ldmatrix applies the swizzle
+// (16-byte chunk c of row r lives at chunk c ^ (r & 7) of its 128-byte row).
 constexpr int TMA_STAGES = 2;  // measured: a third stage costs a resident block per SM and 25 % of the bandwidth
 constexpr int HALVES = D / 64;                                   // 64-column halves of a row
-constexpr int TMA_STAGE_BYTES = 2 * KV_TILE * (D >= 64 ? D : 64) * 2;  // keys and values of 64 tokens
+constexpr int HALF_BYTES = KV_TILE * 128;                        // 64 rows x 128 B
+constexpr int TMA_STAGE_BYTES = 2 * (D >= 64 ? HALVES : 1) * HALF_BYTES;
 
-// Where a stage keeps 16-byte chunk `chunk` of column half `half` of key (kv = 0) or value
-// (kv = 1) row `row` of the tile.  A page arrives as one box [kv][8-row group][half][8 x 128 B]
-// (see make_page_map); page p of the tile lies p * 2 * page_size * D * 2 bytes into the stage.
-__device__ __forceinline__ const bf16* sw_addr(const unsigned char* stage, int page_shift, int kv,
-                                               int row, int half, int chunk) {
-  const int page = row >> page_shift, r = row & ((1 << page_shift) - 1);
-  const int page_bytes = (2 << page_shift) * D * 2;
-  const int off = page * page_bytes + kv * (page_bytes >> 1) + (((r >> 3) * HALVES + half) << 10) +
-                  ((r & 7) << 7) + ((chunk ^ (r & 7)) << 4);
-  return reinterpret_cast<const bf16*>(stage + off);
+__device__ __forceinline__ const bf16* sw_addr(const bf16* half_base, int row, int chunk) {
+  return half_base + row * 64 + ((chunk ^ (row & 7)) << 3);
 }
 
-// S = Q K^T for one warp's 16 keys (rows row0..row0+15 of the stage).
-__device__ __forceinline__ void qk_tile_sw(float (&s)[2][4], const bf16* sQ, const unsigned char* stage,
-                                           int page_shift, int row0) {
+// S = Q K^T for one warp's 16 keys (rows row0..row0+15 of the stage's key halves).
+__device__ __forceinline__ void qk_tile_sw(float (&s)[2][4], const bf16* sQ, const bf16* sKhalves,
+                                           int row0) {
   const int lane = threadIdx.x & 31;
 #pragma unroll
   for (int nt = 0; nt < 2; ++nt)
@@ -528,7 +520,7 @@ __device__ __forceinline__ void qk_tile_sw(float (&s)[2][4], const bf16* sQ, con
     ldsm_x4(a, sQ + ((lane & 7) + 8 * ((lane >> 3) & 1)) * STRIDE + ks * 16 + 8 * (lane >> 4));
     const int row = row0 + (lane & 7) + 8 * (lane >> 4);
     const int chunk = (ks & 3) * 2 + ((lane >> 3) & 1);
-    ldsm_x4(b, sw_addr(stage, page_shift, 0, row, ks >> 2, chunk));
+    ldsm_x4(b, sw_addr(sKhalves + (ks >> 2) * (HALF_BYTES / 2), row, chunk));
     mma_bf16(s[0], a, b[0], b[1]);
     mma_bf16(s[1], a, b[2], b[3]);
   }
@@ -536,7 +528,7 @@ __device__ __forceinline__ void qk_tile_sw(float (&s)[2][4], const bf16* sQ, con
 
 // o += P V for one warp's 16 keys.
 __device__ __forceinline__ void pv_tile_sw(float (&o)[D / 8][4], const float (&s)[2][4],
-                                           const unsigned char* stage, int page_shift, int row0) {
+                                           const bf16* sVhalves, int row0) {
   const int lane = threadIdx.x & 31;
   uint32_t a[4];
   a[0] = pack_bf16(s[0][0], s[0][1]);
@@ -548,7 +540,7 @@ __device__ __forceinline__ void pv_tile_sw(float (&o)[D / 8][4], const float (&s
   for (int dp = 0; dp < D / 16; ++dp) {
     uint32_t b[4];
     const int chunk = (dp & 3) * 2 + (lane >> 4);
-    ldsm_x4_trans(b, sw_addr(stage, page_shift, 1, row, dp >> 2, chunk));
+    ldsm_x4_trans(b, sw_addr(sVhalves + (dp >> 2) * (HALF_BYTES / 2), row, chunk));
     mma_bf16(o[2 * dp], a, b[0], b[1]);
     mma_bf16(o[2 * dp + 1], a, b[2], b[3]);
   }
@@ -633,17 +625,22 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, const bf16*
     const int j0 = (tile_a + i) * KV_TILE + lane * page_size;
     return (j0 <= pos && j0 + page_size - 1 >= k_lo_all) ? table[j0 / page_size] : -1;
   };
-  const int page_shift = __ffs(page_size) - 1;  // the launcher admits powers of two only
   auto issue = [&](int i, int page) {
     const int st = i % TMA_STAGES;
-    const uint32_t dst = stages0 + st * TMA_STAGE_BYTES + lane * page_size * D * 4;
+    const uint32_t dst0 = stages0 + st * TMA_STAGE_BYTES + lane * page_size * 128;
     const int n_boxes = __popc(__ballot_sync(0xffffffffu, page >= 0));
     if (lane == 0)
-      mbar_expect_tx(full0 + 8 * st, (uint32_t)n_boxes * page_size * D * 4u);
+      mbar_expect_tx(full0 + 8 * st, (uint32_t)n_boxes * 2u * HALVES * page_size * 128u);
     __syncwarp();
-    if (page >= 0)  // keys and values of the page, every column, in one copy
-      tma_load_5d(dst, &pool_map, full0 + 8 * st, 0, 0, 0,
-                  ((page * 2) * n_kv_heads + kvh) * (page_size >> 3), 0);
+    if (page >= 0) {
+      const int krow = ((page * 2) * n_kv_heads + kvh) * page_size;
+      const int vrow = krow + n_kv_heads * page_size;
+#pragma unroll
+      for (int h = 0; h < HALVES; ++h) {
+        tma_load_2d(dst0 + h * HALF_BYTES, &pool_map, full0 + 8 * st, h * 64, krow);
+        tma_load_2d(dst0 + (HALVES + h) * HALF_BYTES, &pool_map, full0 + 8 * st, h * 64, vrow);
+      }
+    }
   };
   int page_next = -1;
   if (warp == 0) {
@@ -684,11 +681,12 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, const bf16*
       ok = false;
       break;
     }
-    const unsigned char* stage = stages_ptr + st * TMA_STAGE_BYTES;
+    const bf16* sK = reinterpret_cast<const bf16*>(stages_ptr + st * TMA_STAGE_BYTES);
+    const bf16* sV = sK + HALVES * (HALF_BYTES / 2);
     const int key0 = (tile_a + i) * KV_TILE + warp * 16;
     if (key0 <= pos && key0 + 15 >= k_lo_all) {
       float s[2][4];
-      qk_tile_sw(s, sQ, stage, page_shift, warp * 16);
+      qk_tile_sw(s, sQ, sK, warp * 16);
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
@@ -698,7 +696,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, const bf16*
           s[nt][e] = in ? s[nt][e] * scale_log2 : -INFINITY;
         }
       softmax_update<2>(s, m, l, o);
-      pv_tile_sw(o, s, stage, page_shift, warp * 16);
+      pv_tile_sw(o, s, sV, warp * 16);
     }
     __syncwarp();
     if (lane == 0) mbar_arrive(empty0 + 8 * st);
@@ -870,7 +868,9 @@ SI_API int si_attn_decode(const void* q, int q_stride, const void* pool, int n_p
                           (page_size & (page_size - 1)) == 0 && n_pages > 0 &&
                           (((uintptr_t)pool) & 15) == 0;
   CUtensorMap pool_map;
-  if (tma_shapes && si::make_page_map(&pool_map, pool, n_pages, n_kv_heads, page_size, si::D, 2)) {
+  if (tma_shapes &&
+      si::make_bf16_map(&pool_map, pool, (long long)n_pages * 2 * n_kv_heads * page_size, si::D,
+                        si::D, page_size)) {
     static bool tma_configured = false;
     if (!tma_configured) {
       cudaError_t e = cudaFuncSetAttribute(si::attn_decode_tma_kernel,
