@@ -8,11 +8,11 @@
 //
 // Roles per block (192 threads), as in gemm_tc.cu:
 //   warp 0, one lane   TMA producer: its block's 128 x 64 tile of X and (BN/2) x 64 tile of W
-//                      per k-step into a six-stage ring.  Both blocks' loads report their
+//                      per 64 columns of K, two such pairs per stage of a three-stage ring.  Both blocks' loads report their
 //                      bytes to the FIRST block's `full` barrier (cp.async.bulk.tensor with
 //                      .cta_group::2); no load is a multicast.
 //   warp 1, one lane   in the first block only: the MMA issuer.  Four tcgen05.mma (M256 N=BN
-//                      K16) per k-step; tcgen05.commit with a two-block mask frees the stage
+//                      K16) per 64 columns; tcgen05.commit with a two-block mask frees the stage
 //                      in both blocks, and after the last k-step tells both epilogues.
 //   warps 2..5         epilogue of the block's own 128 rows (its own tensor memory); all
 //                      eight epilogue warps of the pair hand the accumulator back to the
@@ -31,11 +31,16 @@ namespace si {
 typedef __nv_bfloat16 bf16;
 
 constexpr int T2_BM = 128;            // rows per block; a tile has 2 * T2_BM
-constexpr int T2_BK = 64, T2_STAGES = 6;
+constexpr int T2_BK = 64;     // columns of one TMA box (a 128-byte swizzled row)
+constexpr int T2_SUB = 2;     // boxes along K per stage: one barrier round per 128 columns (measured: a
+                              // 2048-token prefill takes 12.9 ms with 3 stages of 2 boxes, 13.9 ms with
+                              // 6 of 1, 13.7 ms with 2 of 3)
+constexpr int T2_STAGES = 3;
 constexpr int T2_THREADS = 192;
 constexpr uint32_t T2_A_BYTES = T2_BM * T2_BK * 2;   // 16 KiB
 constexpr uint32_t T2_B_BYTES = 128 * T2_BK * 2;     // 16 KiB reserved: half of at most 256 weight rows
-constexpr uint32_t T2_STAGE_BYTES = T2_A_BYTES + T2_B_BYTES;
+constexpr uint32_t T2_SUB_BYTES = T2_A_BYTES + T2_B_BYTES;
+constexpr uint32_t T2_STAGE_BYTES = T2_SUB * T2_SUB_BYTES;
 constexpr uint32_t T2_TMEM_COLS = 512;
 constexpr uint32_t T2_SMEM_BYTES = T2_STAGES * T2_STAGE_BYTES + 1024 + 256;
 
@@ -100,7 +105,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const uint32_t bars = base + T2_STAGES * T2_STAGE_BYTES;
-  // full[6], empty[6], acc_full[2], acc_empty[2], then the tensor-memory slot
+  // full[stages], empty[stages], acc_full[2], acc_empty[2], then the tensor-memory slot
   const uint32_t full0 = bars, empty0 = bars + 8 * T2_STAGES;
   const uint32_t acc_full0 = bars + 16 * T2_STAGES, acc_empty0 = acc_full0 + 16;
   const uint32_t tmem_slot = acc_empty0 + 16;
@@ -113,7 +118,8 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
   const int tiles_m = (M + 2 * T2_BM - 1) / (2 * T2_BM);
   const int tiles_n = (n_out + TILE_N_OUT - 1) / TILE_N_OUT;
   const int n_tiles = tiles_m * tiles_n;
-  const int k_blocks = (K + T2_BK - 1) / T2_BK;
+  const int k_boxes = (K + T2_BK - 1) / T2_BK;
+  const int k_blocks = (k_boxes + T2_SUB - 1) / T2_SUB;  // stages per tile
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < T2_STAGES; ++s) {
@@ -151,10 +157,13 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
         for (int kb = 0; kb < k_blocks; ++kb, ++it) {
           const uint32_t s = it % T2_STAGES, ph = (it / T2_STAGES) & 1u;
           if (!t2_wait(empty0 + 8 * s, ph ^ 1u, status, T2_TIMEOUT_PRODUCER)) { ok = false; break; }
-          const uint32_t a_dst = base + s * T2_STAGE_BYTES, b_dst = a_dst + T2_A_BYTES;
-          if (rank == 0) mbar_expect_tx(full0 + 8 * s, STAGE_TX_BYTES);
-          tma_load_2d_pair(a_dst, &map_x, full_first + 8 * s, kb * T2_BK, m0);
-          tma_load_2d_pair(b_dst, &map_w, full_first + 8 * s, kb * T2_BK, w_row);
+          const int nsub = k_boxes - kb * T2_SUB < T2_SUB ? k_boxes - kb * T2_SUB : T2_SUB;
+          if (rank == 0) mbar_expect_tx(full0 + 8 * s, STAGE_TX_BYTES * nsub);
+          for (int j = 0; j < nsub; ++j) {
+            const uint32_t a_dst = base + s * T2_STAGE_BYTES + j * T2_SUB_BYTES, b_dst = a_dst + T2_A_BYTES;
+            tma_load_2d_pair(a_dst, &map_x, full_first + 8 * s, (kb * T2_SUB + j) * T2_BK, m0);
+            tma_load_2d_pair(b_dst, &map_w, full_first + 8 * s, (kb * T2_SUB + j) * T2_BK, w_row);
+          }
         }
       }
     }
@@ -172,11 +181,14 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
           const uint32_t s = it % T2_STAGES, ph = (it / T2_STAGES) & 1u;
           if (!t2_wait(full0 + 8 * s, ph, status, T2_TIMEOUT_MMA)) { ok = false; break; }
           tmem_fence_after();
-          const uint32_t a_src = base + s * T2_STAGE_BYTES;
-          const uint64_t da = umma_desc(a_src), db = umma_desc(a_src + T2_A_BYTES);
+          const int nsub = k_boxes - kb * T2_SUB < T2_SUB ? k_boxes - kb * T2_SUB : T2_SUB;
+          for (int j = 0; j < nsub; ++j) {
+            const uint32_t a_src = base + s * T2_STAGE_BYTES + j * T2_SUB_BYTES;
+            const uint64_t da = umma_desc(a_src), db = umma_desc(a_src + T2_A_BYTES);
 #pragma unroll
-          for (int k = 0; k < T2_BK / 16; ++k)
-            umma_bf16_pair(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb | k) != 0 ? 1u : 0u);
+            for (int k = 0; k < T2_BK / 16; ++k)
+              umma_bf16_pair(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb | j | k) != 0 ? 1u : 0u);
+          }
           umma_commit_pair(empty0 + 8 * s);
         }
         if (ok) umma_commit_pair(acc_full0 + 8 * buf);
