@@ -71,13 +71,23 @@ class ClockSampler:
 
     def __init__(self):
         self.samples: list[list[str]] = []
+        self.stamped: list[tuple[float, list[str]]] = []  # (arrival time, fields)
         self.proc = None
+        self.t0 = self.t1 = None
+
+    def mark_start(self):
+        """The timed region starts now: samples from here on count (the tool needs a moment to
+        come up, so it is started before the warm-up and the region is marked)."""
+        self.t0 = time.time()
+
+    def mark_end(self):
+        self.t1 = time.time()
 
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "25"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except OSError:
@@ -88,7 +98,7 @@ class ClockSampler:
         for line in self.proc.stdout:
             parts = [p.strip() for p in line.split(",")]
             if len(parts) == 6:
-                self.samples.append(parts)
+                self.stamped.append((time.time(), parts))
 
     def __exit__(self, *exc):
         if self.proc is not None:
@@ -99,6 +109,9 @@ class ClockSampler:
                 self.proc.kill()
 
     def summary(self) -> dict:
+        lo = self.t0 if self.t0 is not None else 0.0
+        hi = (self.t1 if self.t1 is not None else time.time()) + 0.03
+        self.samples = [p for t, p in self.stamped if lo <= t <= hi] or [p for _, p in self.stamped[-1:]]
         mhz = sorted(int(s[0]) for s in self.samples if s[0].isdigit())
         mx = [int(s[1]) for s in self.samples if s[1].isdigit()]
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
@@ -169,15 +182,17 @@ def time_decode(model, cfg, batch, steps, warmup, sample_clocks=False):
                    sampler._field(d, 4, batch), sampler._field(d, 5, batch), sampler._out[:batch])
 
     sampler.sample(runner.step([StepEntry(b, [1], [0]) for b in range(batch)]), greedy)  # sets params
+    clocks = ClockSampler() if sample_clocks else None
+    if clocks:
+        clocks.__enter__()
     for i in range(warmup):
         one(i)
     torch.cuda.synchronize()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     k0, r0 = ops.launch_count, runner.replayed_kernels
-    clocks = ClockSampler() if sample_clocks else None
-    if clocks:
-        clocks.__enter__()
     torch.cuda.synchronize()
+    if clocks:
+        clocks.mark_start()
     torch.cuda.profiler.start()  # a profiler started with --profile-from-start off sees only this
     start.record()
     for i in range(warmup, warmup + steps):
@@ -186,6 +201,7 @@ def time_decode(model, cfg, batch, steps, warmup, sample_clocks=False):
     torch.cuda.synchronize()
     torch.cuda.profiler.stop()
     if clocks:
+        clocks.mark_end()
         clocks.__exit__(None, None, None)
     ms = start.elapsed_time(end) / steps
     launches = (ops.launch_count - k0) + (runner.replayed_kernels - r0)
@@ -254,7 +270,7 @@ def time_prefill(model, cfg, reps=5):
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
