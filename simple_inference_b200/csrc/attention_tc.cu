@@ -380,7 +380,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
       const float w0 = (m0 == -INFINITY) ? 0.0f : ex2_approx(m0 - mm);
       const float w1 = (!two || m1 == -INFINITY) ? 0.0f : ex2_approx(m1 - mm);
       float inv = 1.0f / (xsum[0][row] * w0 + xsum[1][row] * w1);
-      if (!ok) inv = __int_as_float(0x7fc00000);
+      if (!ok || *reinterpret_cast<volatile int*>(&failed)) inv = __int_as_float(0x7fc00000);  // make it visible
       bf16* dst = out + (long long)(tok0 + row) * out_stride + (long long)h * HD + set * 64;
 #pragma unroll 1
       for (int c = 0; c < 2; ++c) {

@@ -93,6 +93,46 @@ __global__ void rmsnorm_kernel(float* __restrict__ residual, const TA* __restric
   }
 }
 
+// The same for rows that fit the block at 8 elements a thread (hidden a multiple of 8, at most
+// 8 * blockDim.x): the row stays in registers between the two passes, and the gain is loaded
+// before the sum is known, so a block has one round trip to memory instead of two.
+template <typename TA, typename TW>
+__global__ void rmsnorm_row_in_registers_kernel(float* __restrict__ residual, const TA* __restrict__ delta,
+                                                const TW* __restrict__ weight, const int* __restrict__ rows,
+                                                TA* __restrict__ out, int hidden, float eps) {
+  __shared__ float red[32];
+  const int i = threadIdx.x * 8;
+  const bool mine = i < hidden;
+  float w[8];
+  if (mine) load8<TW>(weight + i, w);  // the gain is not written by any kernel: fetch it before waiting
+  pdl_wait();
+  pdl_trigger();
+  const int r = blockIdx.x;
+  const int src = rows ? rows[r] : r;
+  float* res = residual + (size_t)src * hidden;
+  float x[8];
+  float ss = 0.0f;
+  if (mine) {
+    load8<float>(res + i, x);
+    if (delta) {
+      float d[8];
+      load8<TA>(delta + (size_t)src * hidden + i, d);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) x[j] += d[j];
+      if (rows == nullptr) store8<float>(res + i, x);
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) ss += x[j] * x[j];
+  }
+  const float total = block_sum(ss, red);
+  const float rstd = rsqrtf(total / (float)hidden + eps);
+  if (mine) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) x[j] = (x[j] * rstd) * w[j];
+    store8<TA>(out + (size_t)r * hidden + i, x);
+  }
+}
+
 // ------------------------------------------------------------------- SwiGLU
 // gu is [rows, 2*inter]: gate in columns [0, inter), up in [inter, 2*inter).
 template <typename T, bool VEC>
@@ -155,6 +195,11 @@ static int launch_rmsnorm(float* residual, const void* delta, const void* weight
   int threads = (hidden / per_thread + 31) / 32 * 32;
   if (threads > 512) threads = 512;
   if (threads < 64) threads = 64;
+  if (vec && hidden <= threads * 8) {
+    SI_LAUNCH((si::rmsnorm_row_in_registers_kernel<TA, TW>), n_rows, threads, 0, stream, residual,
+              (const TA*)delta, (const TW*)weight, rows, (TA*)out, hidden, eps);
+    return SI_OK;
+  }
   SI_LAUNCH(kern, n_rows, threads, smem, stream, residual, (const TA*)delta, (const TW*)weight,
             rows, (TA*)out, hidden, eps);
   return SI_OK;
