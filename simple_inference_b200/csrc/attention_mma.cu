@@ -581,7 +581,11 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, const bf16*
     }
     mbar_init_fence();
   }
-  pdl_wait();
+  // The step's batch description (positions, block tables) was copied to the device before
+  // any kernel of the step began, and pages below the current position were written by earlier
+  // steps: this block reads them, and fetches its first keys, BEFORE it waits for the preceding
+  // kernel.  Only the tile that holds the current position (whose key and value that kernel
+  // writes) and the query wait.
   const int seq = single_seqs[blockIdx.x];
   const int tok = cu_q[seq];
   const int pos = positions[tok];
@@ -609,12 +613,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, const bf16*
     }
   }
   fence_proxy_async_smem();
-
-  // Q rows by cp.async: one per query head of the chunk, the rest zero
-  if (n_my > 0) load_q_rows(sQ, q + (long long)tok * q_stride + (long long)head0 * D, D, n_heads_here, 16);
-  cp_async_commit();
-  cp_async_wait<0>();
-  __syncthreads();  // barriers initialised, stages zeroed, Q in place
+  __syncthreads();  // barriers initialised, stages zeroed
 
   // Warp 0 issues the boxes of tile number `i` of this block into stage i % TMA_STAGES: lane pg
   // looks up and fetches page pg of the tile, so a tile's table reads are in flight together
@@ -643,15 +642,26 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, const bf16*
     }
   };
   int page_next = -1;
+  int first[TMA_STAGES];
   if (warp == 0) {
-    int first[TMA_STAGES];
 #pragma unroll
     for (int i = 0; i < TMA_STAGES; ++i) first[i] = lookup(i);
 #pragma unroll
     for (int i = 0; i < TMA_STAGES - 1; ++i)
-      if (i < n_my) issue(i, first[i]);
+      if (i < n_my && tile_a + i != tile_end - 1) issue(i, first[i]);  // old keys: no need to wait
     page_next = first[TMA_STAGES - 1];
   }
+  pdl_wait();
+  if (warp == 0) {
+#pragma unroll
+    for (int i = 0; i < TMA_STAGES - 1; ++i)
+      if (i < n_my && tile_a + i == tile_end - 1) issue(i, first[i]);
+  }
+  // Q rows by cp.async: one per query head of the chunk, the rest zero
+  if (n_my > 0) load_q_rows(sQ, q + (long long)tok * q_stride + (long long)head0 * D, D, n_heads_here, 16);
+  cp_async_commit();
+  cp_async_wait<0>();
+  __syncthreads();  // Q in place
 
   float o[D / 8][4];
 #pragma unroll
