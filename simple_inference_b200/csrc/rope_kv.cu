@@ -26,8 +26,9 @@ __global__ void rope_kv_store_kernel(T* __restrict__ qkv, const int* __restrict_
                                      int n_q_heads, int n_kv_heads, int head_dim, int page_size,
                                      int write_kv) {
   extern __shared__ float cs[];  // cos[half], sin[half]
-  pdl_wait();
   pdl_trigger();
+  // positions, frequencies and slots were on the device before the step's first kernel: the
+  // angles are worked out while the projection before this kernel is still finishing
   const int t = blockIdx.x;
   const int half = head_dim >> 1;
   float* s_cos = cs;
@@ -40,6 +41,8 @@ __global__ void rope_kv_store_kernel(T* __restrict__ qkv, const int* __restrict_
     s_cos[i] = c;
     s_sin[i] = s;
   }
+  const int slot = write_kv ? kv_slots[t] : 0;
+  pdl_wait();
   __syncthreads();
 
   const int row_width = (n_q_heads + 2 * n_kv_heads) * head_dim;
@@ -65,7 +68,6 @@ __global__ void rope_kv_store_kernel(T* __restrict__ qkv, const int* __restrict_
   }
   if (!write_kv) return;
 
-  const int slot = kv_slots[t];
   const int page = slot / page_size, off = slot - page * page_size;
   const size_t head_stride = (size_t)page_size * head_dim;
   T* kpage = pool + ((size_t)page * 2 + 0) * n_kv_heads * head_stride + (size_t)off * head_dim;
