@@ -581,6 +581,10 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, const bf16*
     }
     mbar_init_fence();
   }
+  // The kernels after this one (the join of the splits, then the output projection) are let in
+  // at once: the projection's blocks fit beside these and fetch their first weights meanwhile
+  // (measured: 1.2 % of a decode step at batch 8).
+  pdl_trigger();
   // The step's batch description (positions, block tables) was copied to the device before
   // any kernel of the step began, and pages below the current position were written by earlier
   // steps: this block reads them, and fetches its first keys, BEFORE it waits for the preceding
@@ -712,7 +716,6 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, const bf16*
     if (lane == 0) mbar_arrive(empty0 + 8 * st);
   }
   __syncthreads();  // every warp has left the stages: the space is reused for the merge
-  pdl_trigger();
   const bool bad = failed != 0;
 
   float* wm = reinterpret_cast<float*>(stages_ptr);

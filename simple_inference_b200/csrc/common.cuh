@@ -41,10 +41,14 @@ namespace si {
 // it before it reads or writes anything another kernel touches (weights are
 // never written, so a product may request its first weights before waiting).
 // pdl_trigger() lets the next kernel of the stream be scheduled once all blocks
-// of this one have passed it; kernels call it when their main loop is done, so
-// that the successor's launch and prologue overlap this kernel's tail, and no
-// more than one successor is ever parked on the SMs.  A captured CUDA graph
-// keeps these edges.
+// of this one have passed it.  The products call it when their main loop is done, so
+// that the successor's launch and prologue overlap their tail and the blocks of their
+// last wave are not kept off the SMs by parked successors; short kernels (norms, RoPE,
+// the join of attention splits) call it at once, and so does decode attention, whose
+// blocks leave room for the output projection to come in and fetch its first weights.
+// Whatever a kernel needs that no kernel of the step writes (weights, the step's batch
+// description, keys of earlier positions) it fetches BEFORE pdl_wait().  A captured CUDA
+// graph keeps these edges.
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ void pdl_trigger() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
