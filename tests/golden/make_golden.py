@@ -83,7 +83,9 @@ def reference_logits(ref_root: str, cfg: dict, w: dict, ids: list[int]) -> torch
 
 
 def main() -> None:
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: python tests/golden/make_golden.py <folder of the reference project>")
+    ref_root = sys.argv[1]
     here = Path(__file__).resolve().parent
     for name, cfg in (("A", TINY_A), ("B", TINY_B)):
         cfg = dict(cfg, torch_dtype="float32")
