@@ -112,20 +112,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     tmem_fence_before();
   }
-  // The ring starts as zeros: rows of pages that are not loaded meet P = 0 and must be finite
-  // (later a slot holds an earlier tile's keys or values, which are finite too)
-  {
-    uint4* z = reinterpret_cast<uint4*>(base_ptr + TILE_BYTES);
-    for (int i = threadIdx.x; i < (int)(RING * TILE_BYTES / 16); i += ATC_THREADS)
-      z[i] = make_uint4(0, 0, 0, 0);
-  }
-  fence_proxy_async_smem();
-  __syncthreads();
-  tmem_fence_after();
-  const uint32_t tmem_base = *tmem_slot_ptr;
-  pdl_wait();
-
-  // ---- this block's tile
+  // ---- this block's tile (the step's batch description was on the device before its first
+  // kernel: read it before waiting for the kernel that wrote Q, K and V)
   const int tile_id = blockIdx.y;  // the host lists the longest tiles first; heads vary fastest
   const int seq = tile_seq[tile_id];
   const int tok0 = cu_q[seq] + tile_start[tile_id];
@@ -139,6 +127,25 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
   const int tile_first = k_lo / TK, tile_last = k_hi / TK;
   const int n_tiles = tile_last - tile_first + 1;
   const int* table = block_table + (long long)seq * table_stride;
+
+  // Rows of pages that are not loaded (past the last key, before the window) meet P = 0 and
+  // must hold finite numbers.  A slot that an earlier tile filled does (keys and values are
+  // finite); only a slot whose FIRST tile is such a partial one is cleared here.
+  for (int slot = 0; slot < RING && slot < 2 * n_tiles; ++slot) {
+    const int i = slot;  // the item that uses the slot first
+    const bool is_v = i != 0 && ((i & 1) == 0 || i == 2 * n_tiles - 1);
+    const int t = i == 0 ? 0 : (is_v ? (i == 2 * n_tiles - 1 ? n_tiles - 1 : (i - 2) / 2) : (i + 1) / 2);
+    const bool partial = (t == n_tiles - 1 && (k_hi + 1) % TK != 0) || (t == 0 && k_lo % TK != 0);
+    if (partial) {
+      uint4* z = reinterpret_cast<uint4*>(base_ptr + TILE_BYTES + slot * TILE_BYTES);
+      for (int j = threadIdx.x; j < (int)(TILE_BYTES / 16); j += ATC_THREADS) z[j] = make_uint4(0, 0, 0, 0);
+    }
+  }
+  fence_proxy_async_smem();
+  __syncthreads();
+  tmem_fence_after();
+  const uint32_t tmem_base = *tmem_slot_ptr;
+  pdl_wait();
 
   // Tensor memory: S of tile t in columns [128 b, 128 b + 128) with b = t & 1; P of tile t,
   // bfloat16 pairs, over the first 64 columns of the same buffer once S has been read;
