@@ -304,6 +304,42 @@ def rope_kv_store(qkv: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Te
                                    1 if write_kv else 0, _dt(qkv), _stream()), "rope_kv_store")
 
 
+def can_fuse_projection_rope(x: torch.Tensor, weight: torch.Tensor, qkv: torch.Tensor) -> bool:
+    """Whether ``linear_rope_kv_store`` takes these operands: bfloat16 and few enough rows for
+    the weight-streaming kernel."""
+    return _skinny_ok(x, weight) and qkv.dtype == torch.bfloat16
+
+
+def linear_rope_kv_store(x: torch.Tensor, w_qkv: torch.Tensor, qkv: torch.Tensor,
+                         positions: torch.Tensor, inv_freq: torch.Tensor,
+                         kv_slots: torch.Tensor | None, pool: torch.Tensor | None,
+                         num_q_heads: int, num_kv_heads: int, head_dim: int, page_size: int,
+                         write_kv: bool) -> None:
+    """``linear(x, w_qkv)`` and ``rope_kv_store`` in one kernel, for up to 16 tokens.
+
+    Rotated queries land in the first ``num_q_heads*head_dim`` columns of ``qkv``; keys and
+    values go to the pool only (the other columns of ``qkv`` are not written)."""
+    _dev(x, w_qkv, qkv, positions, inv_freq, kv_slots, pool)
+    _i32(positions, "positions")
+    _i32(kv_slots, "kv_slots")
+    m, k = x.shape
+    width = (num_q_heads + 2 * num_kv_heads) * head_dim
+    if not can_fuse_projection_rope(x, w_qkv, qkv) or w_qkv.shape != (width, k) \
+            or qkv.shape != (m, width) or w_qkv.dtype != torch.bfloat16 or positions.numel() < m:
+        raise KernelError("linear_rope_kv_store: operands do not fit (see can_fuse_projection_rope)")
+    if inv_freq.dtype != torch.float32 or inv_freq.numel() != head_dim // 2:
+        raise KernelError("linear_rope_kv_store: inv_freq must be float32 of head_dim/2 entries")
+    if write_kv:
+        if pool is None or kv_slots is None or pool.dtype != qkv.dtype or kv_slots.numel() < m:
+            raise KernelError("linear_rope_kv_store: pool and kv_slots needed, pool in qkv's dtype")
+        if tuple(pool.shape[1:]) != (2, num_kv_heads, page_size, head_dim):
+            raise KernelError(f"linear_rope_kv_store: pool shape {tuple(pool.shape)} does not fit")
+    _check(core().si_gemm_skinny_rope_kv_bf16(
+        _p(x), x.stride(0), _p(w_qkv), _p(qkv), qkv.stride(0), m, k, _p(positions), _p(inv_freq),
+        _p(kv_slots), _p(pool), num_q_heads, num_kv_heads, head_dim, page_size,
+        1 if write_kv else 0, _stream()), "gemm_skinny_rope_kv")
+
+
 # ---------------------------------------------------------------- attention
 
 def attention_generic(q: torch.Tensor, pool: torch.Tensor, block_table: torch.Tensor,
@@ -469,4 +505,4 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
 
 __all__ = ["KernelError", "KernelBuildError", "embed_gather", "rmsnorm", "swiglu", "linear", "linear_swiglu", "linear_tc",
            "can_fuse_swiglu", "check_status", "status_tensor",
-           "rope_kv_store", "attention_generic", "paged_attention", "attention_prefill_wide", "wide_prefill_fits", "plan_kv_splits", "sample", "core", "attention_library"]
+           "rope_kv_store", "can_fuse_projection_rope", "linear_rope_kv_store", "attention_generic", "paged_attention", "attention_prefill_wide", "wide_prefill_fits", "plan_kv_splits", "sample", "core", "attention_library"]

@@ -67,9 +67,8 @@ class PagedAttention(Mixer):
     def forward(self, x: torch.Tensor, ctx, cache: LayerCache) -> torch.Tensor:
         n = x.shape[0]
         qkv = ctx.ws.get("attn.qkv", (n, self.q_width + 2 * self.kv_width), x.dtype)
-        ops.linear(x, self.w_qkv, qkv)
-        self.position.encode_and_store(qkv, self.num_heads, self.num_kv_heads, self.head_dim,
-                                       ctx, cache)
+        self.position.project_encode_and_store(x, self.w_qkv, qkv, self.num_heads,
+                                               self.num_kv_heads, self.head_dim, ctx, cache)
         mixed = ctx.ws.get("attn.mixed", (n, self.q_width), x.dtype)
         ops.paged_attention(qkv, cache.pool, ctx, cache.group, mixed, self.num_heads,
                             self.num_kv_heads, self.head_dim, self.scale, self.window)

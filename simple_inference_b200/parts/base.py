@@ -154,6 +154,18 @@ class PositionEncoding(Part):
                          head_dim: int, ctx: "StepContext", cache: LayerCache) -> None:
         raise NotImplementedError
 
+    def project_encode_and_store(self, x: torch.Tensor, w_qkv: torch.Tensor, qkv: torch.Tensor,
+                                 num_q_heads: int, num_kv_heads: int, head_dim: int,
+                                 ctx: "StepContext", cache: LayerCache) -> None:
+        """``qkv = x @ w_qkv.T`` followed by ``encode_and_store``.
+
+        An implementation may do both in one kernel; afterwards only the query columns of
+        ``qkv`` and the cache are read, so it need not write the key and value columns.
+        """
+        from .. import ops
+        ops.linear(x, w_qkv, qkv)
+        self.encode_and_store(qkv, num_q_heads, num_kv_heads, head_dim, ctx, cache)
+
 
 class Mixer(Part):
     """Mixes information across the tokens of a request (attention, or a state)."""

@@ -67,6 +67,17 @@ class RotaryEmbedding(PositionEncoding):
         ops.rope_kv_store(qkv, ctx.positions, self.inv_freq, ctx.kv_slots[cache.group], cache.pool,
                           num_q_heads, num_kv_heads, head_dim, cache.page_size, cache.writes)
 
+    def project_encode_and_store(self, x, w_qkv, qkv, num_q_heads, num_kv_heads, head_dim, ctx,
+                                 cache: LayerCache):
+        # a few tokens (decoding): the rotation and the cache write are the projection's epilogue
+        if ops.can_fuse_projection_rope(x, w_qkv, qkv):
+            ops.linear_rope_kv_store(x, w_qkv, qkv, ctx.positions, self.inv_freq,
+                                     ctx.kv_slots[cache.group], cache.pool, num_q_heads,
+                                     num_kv_heads, head_dim, cache.page_size, cache.writes)
+        else:
+            super().project_encode_and_store(x, w_qkv, qkv, num_q_heads, num_kv_heads, head_dim,
+                                             ctx, cache)
+
 
 @register_position_encoding("none")
 class NoPositionEncoding(PositionEncoding):
@@ -83,3 +94,14 @@ class NoPositionEncoding(PositionEncoding):
     def encode_and_store(self, qkv, num_q_heads, num_kv_heads, head_dim, ctx, cache: LayerCache):
         ops.rope_kv_store(qkv, ctx.positions, self.inv_freq, ctx.kv_slots[cache.group], cache.pool,
                           num_q_heads, num_kv_heads, head_dim, cache.page_size, cache.writes)
+
+    def project_encode_and_store(self, x, w_qkv, qkv, num_q_heads, num_kv_heads, head_dim, ctx,
+                                 cache: LayerCache):
+        # a few tokens (decoding): the rotation and the cache write are the projection's epilogue
+        if ops.can_fuse_projection_rope(x, w_qkv, qkv):
+            ops.linear_rope_kv_store(x, w_qkv, qkv, ctx.positions, self.inv_freq,
+                                     ctx.kv_slots[cache.group], cache.pool, num_q_heads,
+                                     num_kv_heads, head_dim, cache.page_size, cache.writes)
+        else:
+            super().project_encode_and_store(x, w_qkv, qkv, num_q_heads, num_kv_heads, head_dim,
+                                             ctx, cache)

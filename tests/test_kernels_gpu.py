@@ -151,6 +151,47 @@ def test_rope_and_page_write(ops, dt, hq, hkv, d, ps):
     assert torch.equal(q3[:, :hq * d], q1[:, :hq * d]) and torch.equal(pool, before)
 
 
+@pytest.mark.parametrize("hq,hkv,d,ps,hidden,lens,starts", [
+    (4, 2, 16, 4, 64, [1, 1, 1], [0, 90, 11]), (6, 3, 48, 8, 120, [1] * 8, [5, 0, 300, 7, 63, 64, 2, 9]),
+    (24, 8, 128, 16, 3072, [1] * 5, [2047, 0, 15, 16, 700]), (5, 5, 80, 3, 200, [7, 2, 1, 3, 3], [0, 40, 3, 8, 100]),
+    (2, 2, 256, 2, 72, [1, 2], [100, 3]), (3, 1, 32, 16, 96, [9], [20])])
+def test_projection_with_rotation_and_page_write_in_one_kernel(ops, hq, hkv, d, ps, hidden, lens, starts):
+    """Up to 16 tokens: the stacked projection, the rotation and the cache write as one kernel
+    against the two kernels apart (same arithmetic) and against the float32 twin."""
+    dt = torch.bfloat16
+    qkv, pool, ctx, n = paged_case(lens, starts, ps, hq, hkv, d, dt)
+    assert n <= 16
+    g = torch.Generator().manual_seed(n * 31 + d)
+    x = torch.randn(n, hidden, generator=g).to(dev(), dt)
+    w = (torch.randn((hq + 2 * hkv) * d, hidden, generator=g) / math.sqrt(hidden)).to(dev(), dt)
+    inv = plain_llama.rope_frequencies(d, 10000.0, None).to(dev())
+    pool.zero_()
+    pool_apart, pool_twin = pool.clone(), pool.clone()
+    assert ops.can_fuse_projection_rope(x, w, qkv)
+    fused = torch.zeros_like(qkv)
+    ops.linear_rope_kv_store(x, w, fused, ctx.positions, inv, ctx.kv_slots[0], pool, hq, hkv, d, ps, True)
+    apart = torch.empty_like(qkv)
+    ops.linear(x, w, apart)
+    projected = apart.clone()
+    ops.rope_kv_store(apart, ctx.positions, inv, ctx.kv_slots[0], pool_apart, hq, hkv, d, ps, True)
+    q = slice(0, hq * d)
+    assert (fused[:, q].float() - apart[:, q].float()).abs().max() <= 2 ** -7 * apart[:, q].float().abs().max()
+    assert (fused[:, q] != apart[:, q]).float().mean() < 0.01      # one rounding of a sum apart at most
+    assert (pool.float() - pool_apart.float()).abs().max() <= 2 ** -7 * pool_apart.float().abs().max()
+    assert (pool != pool_apart).float().mean() < 0.01
+    assert float(fused[:, hq * d:].abs().sum()) == 0                # keys and values go to the pages only
+    assert float(pool[-1].abs().sum()) == 0                          # scratch untouched
+    twin = projected.clone()
+    twin_ops.rope_kv_store(twin, ctx.positions, inv, ctx.kv_slots[0], pool_twin, hq, hkv, d, ps, True)
+    assert (fused[:, q].float() - twin[:, q].float()).abs().max() < 4e-2
+    assert (pool.float() - pool_twin.float()).abs().max() < 4e-2
+    # without the write only the queries come out
+    before = pool.clone()
+    again = torch.zeros_like(qkv)
+    ops.linear_rope_kv_store(x, w, again, ctx.positions, inv, None, None, hq, hkv, d, ps, False)
+    assert torch.equal(again, fused) and torch.equal(pool, before)
+
+
 @pytest.mark.parametrize("hq,hkv,d,ps,window", [(4, 2, 16, 4, None), (6, 3, 48, 8, None),
                                                  (3, 1, 32, 16, 7), (24, 8, 128, 16, None),
                                                  (2, 2, 256, 2, None), (5, 5, 80, 3, 33)])
