@@ -176,10 +176,17 @@ class BatchBuilder:
         # so that a request that keeps its row from step to step only appends its new pages
         self._row_owner: list[list[tuple[int, int] | None]] = [
             [None] * max_seqs for _ in range(self.n_groups)]
+        # views of the two buffers are made once per distinct set of sizes: slicing a torch
+        # tensor costs more than filling a decode step's numbers
+        self._host_views: dict[str, np.ndarray] = {}
+        self._device_views: dict[tuple, dict] = {}
 
     def _h(self, name: str) -> np.ndarray:
-        o, n = self._off[name]
-        return self.host_np[o:o + n]
+        v = self._host_views.get(name)
+        if v is None:
+            o, n = self._off[name]
+            v = self._host_views[name] = self.host_np[o:o + n]
+        return v
 
     def _d(self, name: str, n: int | None = None) -> torch.Tensor:
         o, cap = self._off[name]
@@ -305,19 +312,26 @@ class BatchBuilder:
             self._copied.record()
             self._copy_pending = True
 
+        sizes = (N, S, r, n_single, n_tiles, n_pairs, len(wide))
+        views = self._device_views.get(sizes)
+        if views is None:
+            if len(self._device_views) >= 512:
+                self._device_views.clear()
+            views = self._device_views[sizes] = dict(
+                token_ids=self._d("token_ids", N), positions=self._d("positions", N),
+                tok_seq=self._d("tok_seq", N),
+                kv_slots=[self._d(f"kv_slots{g}", N) for g in range(self.n_groups)],
+                cu_q=self._d("cu_q", S + 1), seq_slots=self._d("seq_slots", S),
+                block_tables=[self._d(f"block_table{g}").view(self.max_seqs, self.table_len[g])[:S]
+                              for g in range(self.n_groups)],
+                logit_rows=self._d("logit_rows", r),
+                single_seqs=self._d("single_seqs", n_single),
+                tile_seq=self._d("tile_seq", n_tiles), tile_start=self._d("tile_start", n_tiles),
+                tile_pairs=self._d("tile_pairs", 2 * n_pairs),
+                wide_seq=self._d("wide_seq", len(wide)), wide_start=self._d("wide_start", len(wide)))
         return StepContext(
-            n_tokens=N, n_seqs=S, num_logit_rows=r,
-            token_ids=self._d("token_ids", N), positions=self._d("positions", N),
-            tok_seq=self._d("tok_seq", N),
-            kv_slots=[self._d(f"kv_slots{g}", N) for g in range(self.n_groups)],
-            cu_q=self._d("cu_q", S + 1), seq_slots=self._d("seq_slots", S),
-            block_tables=[self._d(f"block_table{g}").view(self.max_seqs, self.table_len[g])[:S]
-                          for g in range(self.n_groups)],
-            logit_rows=self._d("logit_rows", r),
-            single_seqs=self._d("single_seqs", n_single), n_single=n_single,
-            tile_seq=self._d("tile_seq", n_tiles), tile_start=self._d("tile_start", n_tiles),
-            n_tiles=n_tiles, tile_pairs=self._d("tile_pairs", 2 * n_pairs), n_pairs=n_pairs,
-            wide_seq=self._d("wide_seq", len(wide)), wide_start=self._d("wide_start", len(wide)),
-            n_wide=len(wide), max_kv_len=max(kv_lens) if kv_lens else 0,
-            max_q_len=max(q_lens) if q_lens else 0, max_seqs=self.max_seqs, ws=ws, q_lens=q_lens, kv_lens=kv_lens,
+            n_tokens=N, n_seqs=S, num_logit_rows=r, n_single=n_single, n_tiles=n_tiles,
+            n_pairs=n_pairs, n_wide=len(wide), max_kv_len=max(kv_lens) if kv_lens else 0,
+            max_q_len=max(q_lens) if q_lens else 0, max_seqs=self.max_seqs, ws=ws, q_lens=q_lens,
+            kv_lens=kv_lens, **views,
         )

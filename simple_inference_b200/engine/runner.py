@@ -54,6 +54,7 @@ class ModelRunner:
         self.cuda_graphs = cuda_graphs and rt.device.type == "cuda"
         self._graphs: dict[int, tuple[torch.cuda.CUDAGraph, torch.Tensor]] = {}
         self._graph_kernels: dict[int, int] = {}   # bucket -> kernels of this package in its graph
+        self._logit_rows: dict[tuple[int, int], torch.Tensor] = {}
         self.replayed_kernels = 0                  # kernels launched through graph replays so far
         self._buckets = decode_buckets(max_seqs)
         self.last_context: StepContext | None = None
@@ -110,7 +111,10 @@ class ModelRunner:
         graph, logits = self._graphs[bucket]
         graph.replay()
         self.replayed_kernels += self._graph_kernels[bucket]
-        return logits[:len(entries)]
+        rows = self._logit_rows.get((bucket, len(entries)))
+        if rows is None:   # a view per (bucket, live rows), made once
+            rows = self._logit_rows[(bucket, len(entries))] = logits[:len(entries)]
+        return rows
 
     def _capture(self, bucket: int, ctx: StepContext) -> None:
         """Warm up on a side stream, then record one forward (reference model/cuda_graph.py:62-88).
