@@ -156,7 +156,8 @@ def fill_context(cache, runner, batch, vocab, seed):
     for b in range(batch):
         cache.admit(b, MAX_CONTEXT)
         ids = torch.randint(0, vocab, (DECODE_CONTEXT - 1,), generator=g).tolist()
-        runner.step([StepEntry(b, ids, [])])
+        for i in range(0, len(ids), runner.max_step_tokens):   # in portions the runner takes
+            runner.step([StepEntry(b, ids[i:i + runner.max_step_tokens], [])])
     torch.cuda.synchronize()
 
 
@@ -279,9 +280,17 @@ def main() -> int:
     ap.add_argument("--only", choices=["decode", "prefill"],
                     help="run one part and print a short record (for profiling; not the contract line)")
     ap.add_argument("--eager", action="store_true", help="no CUDA graphs (for kernel-level profiles)")
+    ap.add_argument("--context", type=int, default=None,
+                    help="with --only decode: tokens each request holds (default 2048)")
+    ap.add_argument("--prefill-tokens", type=int, default=None,
+                    help="with --only prefill: length of the prompt (default 2048)")
     args = ap.parse_args()
-    global EAGER
+    global EAGER, DECODE_CONTEXT, PREFILL_TOKENS, MAX_CONTEXT
     EAGER = args.eager
+    if args.only and (args.context or args.prefill_tokens):   # other sizes than the headline's
+        DECODE_CONTEXT = args.context or DECODE_CONTEXT
+        PREFILL_TOKENS = args.prefill_tokens or PREFILL_TOKENS
+        MAX_CONTEXT = max(MAX_CONTEXT, DECODE_CONTEXT + 2048, PREFILL_TOKENS)
 
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -310,8 +319,9 @@ def main() -> int:
 
     if args.only == "decode":
         ms, launches, _, _ = time_decode(model, cfg, args.batch, args.steps, args.warmup)
-        print(json.dumps({"only": "decode", "batch": args.batch, "layers": cfg.num_hidden_layers,
-                          "eager": EAGER, "ms_per_step": round(ms, 4), "launches": launches}))
+        print(json.dumps({"only": "decode", "batch": args.batch, "context": DECODE_CONTEXT,
+                          "layers": cfg.num_hidden_layers, "eager": EAGER,
+                          "ms_per_step": round(ms, 4), "launches": launches}))
         return 0
     if args.only == "prefill":
         pre_ms = time_prefill(model, cfg, reps=max(1, args.steps))
