@@ -3,22 +3,28 @@
 // over the paged cache, with both matrix products as tcgen05.mma and their results in tensor
 // memory.
 //
-// One block per (128-query tile of a sequence, query head); keys in tiles of 128.  Roles:
-//   warp 0             TMA producer: the Q tile once (two 64-column halves, straight from
-//                      the qkv buffer), then per key tile the K and V rows of its pages
-//                      (one cp.async.bulk.tensor box per page: all its rows, both column
-//                      halves, 128-byte swizzle; one lane per page) into a ring of slots that K and V tiles share, in the
-//                      order the products need them; mbarriers count the bytes.
-//   warp 1, one lane   MMA issuer: S = Q K^T (M128 N128, eight K16 steps; Q and K are
-//                      K-major) into one of two S buffers in tensor memory, and
-//                      PV = P V (P is read from tensor memory, where the softmax warps put it
-//                      over the S it came from; V is MN-major: its rows are keys) into one
-//                      of two output buffers (tiles of equal parity add up in the same one).
-//                      S of the next tile is issued before PV of this one, so the tensor
-//                      core works while softmax runs.
+// One block per (128-query tile of a sequence, query head); keys in tiles of 128.  Twelve
+// warps, each kind of work with a thread of its own, because a wait on an mbarrier costs the
+// waiting thread some 200 cycles even when the barrier is already complete, and a thread that
+// makes several such waits per tile sets the pace of the whole block:
+//   warps 0 and 11     TMA producers, one for the key tiles (and the Q tile, once: two
+//                      64-column halves straight from the qkv buffer), one for the value
+//                      tiles: per tile the rows of its pages (one cp.async.bulk.tensor box per
+//                      page: all its rows, both column halves, 128-byte swizzle; one lane per
+//                      page) into a ring of slots that K and V tiles share, in the order the
+//                      products need them; mbarriers count the bytes.  The block-table entries
+//                      of a tile are fetched two tiles ahead (cp.async into shared memory).
+//   warp 1, one lane   issues S = Q K^T (M128 N128, eight K16 steps; Q and K are K-major)
+//                      into one of two S buffers in tensor memory; S(t) follows the
+//                      completion of PV(t-2), which read P from the same buffer.
+//   warp 10, one lane  issues PV = P V (P is read from tensor memory, where the softmax
+//                      warps put it over the S it came from; V is MN-major: its rows are
+//                      keys) into one of two output buffers (tiles of equal parity add up in
+//                      the same one).
 //   warps 2..9         softmax, in two sets of four warps, one thread per query row.  Set b
-//                      owns tiles b, b+2, ...: it reads S with tcgen05.ld (once for the row
-//                      maximum, once for P), masks edge tiles by absolute position, runs the
+//                      owns tiles b, b+2, ...: it reads the row of S with tcgen05.ld (four
+//                      loads, one wait: the softmax lies on the chain S -> P -> PV -> next S
+//                      of its set), masks edge tiles by absolute position, runs the
 //                      online softmax in float32 (kernels/attention_kernel.py:231-241) with
 //                      two-wide fma and ex2.approx, rounds P to bfloat16 (:240) and stores it
 //                      to tensor memory as the next product's A operand.  The set's output
@@ -41,7 +47,8 @@ typedef __nv_bfloat16 bf16;
 constexpr int TQ = 128, TK = 128, HD = 128;
 constexpr uint32_t HALF_BYTES_TC = 128 * 128;        // 128 rows x 64 bf16
 constexpr uint32_t TILE_BYTES = 2 * HALF_BYTES_TC;   // 128 x 128 bf16 = 32 KiB
-constexpr int ATC_THREADS = 320;  // producer warp, MMA warp, eight softmax warps
+constexpr int ATC_THREADS = 384;  // key producer, S issuer, eight softmax warps, P V issuer, value producer
+constexpr int PV_WARP = 10, V_WARP = 11;
 constexpr int RING = 5;           // K and V tiles share one ring of 32 KiB slots
 constexpr uint32_t ATC_SMEM = 1024 + (1 + RING) * TILE_BYTES + 256;  // Q, the ring, barriers
 
@@ -87,6 +94,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
   volatile uint32_t* tmem_slot_ptr =
       reinterpret_cast<volatile uint32_t*>(base_ptr + (1 + RING) * TILE_BYTES + 72);
   __shared__ int failed;
+  __shared__ int tile_pages_of[2][4][32];  // per producer warp: block-table entries of four tiles in turn, one page per lane
   __shared__ float xmax[2][2][TQ];  // [tile parity][part][row]: the two threads of a row trade maxima
   __shared__ float xsum[2][TQ];
 
@@ -151,10 +159,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
   // bfloat16 pairs, over the first 64 columns of the same buffer once S has been read;
   // P V of tile t in columns [256 + 128 b, 256 + 128 b + 128).
 
-  if (warp == 0) {  // ----------------------------------------------------------- TMA producer
-    // Lane i looks up and fetches page i of a key tile, so the table reads of a tile are in
-    // flight together, and those of the next tile while this one's stage is awaited.
-    if (lane == 0) {
+  if (warp == 0 || warp == V_WARP) {  // ------------------------------------------ TMA producers
+    // Two warps, one for the key tiles and one for the value tiles: a tile is one copy per
+    // page, issued lane by lane, and one warp issuing both kinds took as long per tile as all
+    // the rest of the block.  Lane i looks up and fetches page i of a tile.
+    const bool my_kind_is_v = warp == V_WARP;
+    int (*tile_pages)[32] = tile_pages_of[my_kind_is_v ? 1 : 0];
+    if (warp == 0 && lane == 0) {
       mbar_expect_tx(q_full, TILE_BYTES);
       tma_load_2d(sQ, &q_map, q_full, h * HD, tok0);
       tma_load_2d(sQ + HALF_BYTES_TC, &q_map, q_full, h * HD + 64, tok0);
@@ -166,18 +177,32 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
       is_v = i != 0 && ((i & 1) == 0 || i == n_items - 1);
       return i == 0 ? 0 : (is_v ? (i == n_items - 1 ? n_tiles - 1 : (i - 2) / 2) : (i + 1) / 2);
     };
-    auto page_of = [&](int t) {
+    // The block-table entries of tile t travel to shared memory two tiles ahead of their first
+    // use (cp.async, no register waits on them): a load issued when it is needed would put a
+    // trip to L2 into every item of this loop, and the loop sets the pace of the block.
+    auto wanted = [&](int t) {
       const int j0 = (tile_first + t) * TK + lane * page_size;
-      const bool wanted = lane < pages_per_tile && j0 <= k_hi && j0 + page_size - 1 >= k_lo;
-      return wanted ? table[j0 / page_size] : -1;
+      return lane < pages_per_tile && j0 <= k_hi && j0 + page_size - 1 >= k_lo;
     };
-    bool v_next = false;
-    int page_next = n_items > 0 ? page_of(tile_of(0, v_next)) : -1;
+    auto fetch_pages = [&](int t) {
+      if (t < n_tiles && wanted(t)) {
+        const int j0 = (tile_first + t) * TK + lane * page_size;
+        const uint32_t dst = smem_u32(&tile_pages[t & 3][lane]);
+        asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(table + j0 / page_size) : "memory");
+      }
+      asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    fetch_pages(0);
+    fetch_pages(1);
     for (int i = 0; i < n_items; ++i) {
       const int slot = i % RING;
-      const int page = page_next;
-      const bool is_v = v_next;
-      if (i + 1 < n_items) page_next = page_of(tile_of(i + 1, v_next));
+      bool is_v;
+      const int tile = tile_of(i, is_v);
+      if (is_v != my_kind_is_v) continue;
+      // this warp's entries of the tile were asked for two tiles ago
+      fetch_pages(tile + 2);
+      asm volatile("cp.async.wait_group 2;" ::: "memory");
+      const int page = wanted(tile) ? tile_pages[tile & 3][lane] : -1;
       bool ok = true;
       if (i >= RING) ok = mbar_wait_bounded(slot_empty0 + 8 * slot, ((i / RING) - 1) & 1);
       if (!__all_sync(0xffffffffu, ok)) {
@@ -197,17 +222,22 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {  // --------------------------------------------------------- MMA issuer
-      // Issue order S(0), S(1), PV(0), S(2), PV(1), ...  The tensor core runs them in that
-      // order, so S(t+2) overwrites its buffer only after PV(t) has read P(t) from it, and
-      // PV(t) is issued only after the softmax warps have read S(t) and written P(t).
+    if (lane == 0) {  // ------------------------------------------------- issuer of S = Q K^T
+      // Two threads issue the products, one the S = Q K^T of every tile, the other the P V:
+      // a wait on a barrier costs a thread some 200 cycles even when the barrier is complete,
+      // and one thread doing all four waits of a tile kept the tensor core idle half the time.
+      // S(t) overwrites the buffer that P(t-2) was read from, so it follows the completion of
+      // PV(t-2) (the barrier o_full of that buffer); everything else is ordered through the
+      // softmax warps (s_full -> p_full).
       constexpr uint32_t idesc_s = umma_idesc(TQ, TK, false);   // Q K^T: both K-major
-      constexpr uint32_t idesc_o = umma_idesc(TQ, HD, true);    // P V: V is MN-major
       bool ok = mbar_wait_bounded(q_full, 0);
-      auto issue_s = [&](int t) {
+      for (int t = 0; ok && t < n_tiles; ++t) {
         const int b = t & 1;
+        // the keys are usually there long before the buffer is free: that wait comes first
         const int item = k_item(t), slot = item % RING;
-        if (!mbar_wait_bounded(slot_full0 + 8 * slot, (item / RING) & 1)) return false;
+        if (!mbar_wait_bounded(slot_full0 + 8 * slot, (item / RING) & 1)) ok = false;
+        if (ok && t >= 2 && !mbar_wait_bounded(o_full0 + 8 * b, ((t - 2) >> 1) & 1)) ok = false;
+        if (!ok) break;
         tmem_fence_after();
         const uint32_t kbase = ring + slot * TILE_BYTES;
 #pragma unroll
@@ -220,13 +250,20 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
         }
         umma_commit(s_full0 + 8 * b);
         umma_commit(slot_empty0 + 8 * slot);
-        return true;
-      };
-      auto issue_pv = [&](int t) {
+      }
+      if (!ok) atomicExch(&failed, 1);
+    }
+  } else if (warp == PV_WARP) {
+    if (lane == 0) {  // ----------------------------------------------------- issuer of P V
+      // PV(t) is issued once the softmax warps have read S(t) and written P(t) over it.
+      constexpr uint32_t idesc_o = umma_idesc(TQ, HD, true);    // P V: V is MN-major
+      bool ok = true;
+      for (int t = 0; ok && t < n_tiles; ++t) {
         const int b = t & 1;
-        if (!mbar_wait_bounded(p_full0 + 8 * b, (t >> 1) & 1)) return false;
         const int item = v_item(t, n_tiles), slot = item % RING;
-        if (!mbar_wait_bounded(slot_full0 + 8 * slot, (item / RING) & 1)) return false;
+        if (!mbar_wait_bounded(slot_full0 + 8 * slot, (item / RING) & 1)) ok = false;   // values first: see above
+        if (ok && !mbar_wait_bounded(p_full0 + 8 * b, (t >> 1) & 1)) ok = false;
+        if (!ok) break;
         tmem_fence_after();
         const uint32_t vbase = ring + slot * TILE_BYTES;
 #pragma unroll
@@ -238,12 +275,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
         }
         umma_commit(o_full0 + 8 * b);
         umma_commit(slot_empty0 + 8 * slot);
-        return true;
-      };
-      if (ok) ok = issue_s(0);
-      for (int t = 0; ok && t < n_tiles; ++t) {
-        if (t + 1 < n_tiles) ok = issue_s(t + 1);
-        if (ok) ok = issue_pv(t);
       }
       if (!ok) atomicExch(&failed, 1);
     }
@@ -275,9 +306,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
       auto visible = [&](int key) {
         return row_ok && key <= my_pos && (window <= 0 || key > my_pos - window);
       };
-      // pass 1: the row's maximum over the tile.  The chunks are read last to first, each load
-      // under way while the chunk before it is worked on, and chunk 0 stays in registers for pass 2.
-      uint32_t ra[32], rb[32];
+      // The whole row of S comes into registers at once (four loads, one wait): the softmax of a
+      // tile lies on the chain S -> P -> P V -> next S of its set, so the latency of a
+      // tensor-memory load is paid once a tile and P is worked out from the registers.
+      uint32_t r0[32], r1[32], r2[32], r3[32];
       auto mask_chunk = [&](uint32_t (&r)[32], int c) {
         if (need_mask) {
 #pragma unroll
@@ -291,22 +323,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
         for (int i = 2; i < 32; i += 2) a = fmax3(a, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
         return a;
       };
-      tmem_ld32(s_addr + 96, ra);
+      tmem_ld32(s_addr, r0);
+      tmem_ld32(s_addr + 32, r1);
+      tmem_ld32(s_addr + 64, r2);
+      tmem_ld32(s_addr + 96, r3);
       tmem_ld_wait();
-      tmem_ld32(s_addr + 64, rb);
-      mask_chunk(ra, 3);
-      float mx = max_chunk(ra);
-      tmem_ld_wait();
-      tmem_ld32(s_addr + 32, ra);
-      mask_chunk(rb, 2);
-      mx = fmaxf(mx, max_chunk(rb));
-      tmem_ld_wait();
-      tmem_ld32(s_addr, rb);
-      mask_chunk(ra, 1);
-      mx = fmaxf(mx, max_chunk(ra));
-      tmem_ld_wait();
-      mask_chunk(rb, 0);
-      mx = fmaxf(mx, max_chunk(rb));
+      mask_chunk(r0, 0);
+      mask_chunk(r1, 1);
+      mask_chunk(r2, 2);
+      mask_chunk(r3, 3);
+      const float mx = fmaxf(fmaxf(max_chunk(r0), max_chunk(r1)), fmaxf(max_chunk(r2), max_chunk(r3)));
       const float m_new = fmaxf(m_run, mx * scale_log2);
       if (j == 0) {
         m_run = m_new;  // nothing added up yet
@@ -333,8 +359,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
         }
       }
       const float m_use = (m_run == -INFINITY) ? 0.0f : m_run;
-      // pass 2: P = exp2(S * scale - m), rounded to bfloat16, over the S it came from; chunk 0
-      // is still in registers, and each further chunk is loaded while the one before is worked on
+      // P = exp2(S * scale - m), rounded to bfloat16, stored over the S it came from
       const float2 sc2 = make_float2(scale_log2, scale_log2), nm2 = make_float2(-m_use, -m_use);
       float2 acc = make_float2(0.0f, 0.0f);
       auto p_chunk = [&](const uint32_t (&r)[32], int c) {
@@ -347,21 +372,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
           acc = __fadd2_rn(acc, x);
           pk[i] = pack_bf16(x.x, x.y);
         }
-        tmem_st16(s_addr + c * 16, pk);  // 32 keys = 16 packed columns; behind the columns read so far
+        tmem_st16(s_addr + c * 16, pk);  // 32 keys = 16 packed columns
       };
-      tmem_ld32(s_addr + 32, ra);
-      p_chunk(rb, 0);
-      tmem_ld_wait();
-      tmem_ld32(s_addr + 64, rb);
-      mask_chunk(ra, 1);
-      p_chunk(ra, 1);
-      tmem_ld_wait();
-      tmem_ld32(s_addr + 96, ra);
-      mask_chunk(rb, 2);
-      p_chunk(rb, 2);
-      tmem_ld_wait();
-      mask_chunk(ra, 3);
-      p_chunk(ra, 3);
+      p_chunk(r0, 0);
+      p_chunk(r1, 1);
+      p_chunk(r2, 2);
+      p_chunk(r3, 3);
       tmem_st_wait();
       tmem_fence_before();
       __syncwarp();
