@@ -4,10 +4,11 @@
 // memory.
 //
 // One block per (128-query tile of a sequence, query head); keys in tiles of 128.  Twelve
-// warps, each kind of work with a thread of its own, because a wait on an mbarrier costs the
+// warps (the first four, with the light roles, give registers to the eight softmax warps:
+// setmaxnreg), each kind of work with a thread of its own, because a wait on an mbarrier costs the
 // waiting thread some 200 cycles even when the barrier is already complete, and a thread that
 // makes several such waits per tile sets the pace of the whole block:
-//   warps 0 and 11     TMA producers, one for the key tiles (and the Q tile, once: two
+//   warps 0 and 3      TMA producers, one for the key tiles (and the Q tile, once: two
 //                      64-column halves straight from the qkv buffer), one for the value
 //                      tiles: per tile the rows of its pages (one cp.async.bulk.tensor box per
 //                      page: all its rows, both column halves, 128-byte swizzle; one lane per
@@ -17,11 +18,11 @@
 //   warp 1, one lane   issues S = Q K^T (M128 N128, eight K16 steps; Q and K are K-major)
 //                      into one of two S buffers in tensor memory; S(t) follows the
 //                      completion of PV(t-2), which read P from the same buffer.
-//   warp 10, one lane  issues PV = P V (P is read from tensor memory, where the softmax
+//   warp 2, one lane   issues PV = P V (P is read from tensor memory, where the softmax
 //                      warps put it over the S it came from; V is MN-major: its rows are
 //                      keys) into one of two output buffers (tiles of equal parity add up in
 //                      the same one).
-//   warps 2..9         softmax, in two sets of four warps, one thread per query row.  Set b
+//   warps 4..11        softmax, in two sets of four warps, one thread per query row.  Set b
 //                      owns tiles b, b+2, ...: it reads the row of S with tcgen05.ld (four
 //                      loads, one wait: the softmax lies on the chain S -> P -> PV -> next S
 //                      of its set), masks edge tiles by absolute position, runs the
@@ -48,7 +49,8 @@ constexpr int TQ = 128, TK = 128, HD = 128;
 constexpr uint32_t HALF_BYTES_TC = 128 * 128;        // 128 rows x 64 bf16
 constexpr uint32_t TILE_BYTES = 2 * HALF_BYTES_TC;   // 128 x 128 bf16 = 32 KiB
 constexpr int ATC_THREADS = 384;  // key producer, S issuer, eight softmax warps, P V issuer, value producer
-constexpr int PV_WARP = 10, V_WARP = 11;
+constexpr int PV_WARP = 2, V_WARP = 3, SOFTMAX_WARP0 = 4;  // warps 0..3: the light roles, one warpgroup
+constexpr int LIGHT_REGS = 56, SOFTMAX_REGS = 224;     // 128 x 56 + 256 x 224 registers = 63 K of the SM's 64 K
 constexpr int RING = 5;           // K and V tiles share one ring of 32 KiB slots
 constexpr uint32_t ATC_SMEM = 1024 + (1 + RING) * TILE_BYTES + 256;  // Q, the ring, barriers
 
@@ -153,12 +155,17 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
   __syncthreads();
   tmem_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
+  // The softmax warps hold a row of S (128 values) and the P they make of it: the first
+  // warpgroup (producers and issuers) hands them the registers it does not need.
+  // (the two instructions stand at the head of the two branches below)
   pdl_wait();
 
   // Tensor memory: S of tile t in columns [128 b, 128 b + 128) with b = t & 1; P of tile t,
   // bfloat16 pairs, over the first 64 columns of the same buffer once S has been read;
   // P V of tile t in columns [256 + 128 b, 256 + 128 b + 128).
 
+  if (warp < SOFTMAX_WARP0) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(LIGHT_REGS));
   if (warp == 0 || warp == V_WARP) {  // ------------------------------------------ TMA producers
     // Two warps, one for the key tiles and one for the value tiles: a tile is one copy per
     // page, issued lane by lane, and one warp issuing both kinds took as long per tile as all
@@ -253,7 +260,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
       }
       if (!ok) atomicExch(&failed, 1);
     }
-  } else if (warp == PV_WARP) {
+  } else {  // warp == PV_WARP
     if (lane == 0) {  // ----------------------------------------------------- issuer of P V
       // PV(t) is issued once the softmax warps have read S(t) and written P(t) over it.
       constexpr uint32_t idesc_o = umma_idesc(TQ, HD, true);    // P V: V is MN-major
@@ -278,7 +285,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
       }
       if (!ok) atomicExch(&failed, 1);
     }
+  }
   } else {  // ------------------------------------------------------- softmax and epilogue
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(SOFTMAX_REGS));
     // Two sets of four warps; set b owns the tiles b, b + 2, ... (S buffer b, output buffer b)
     // and runs its own online softmax over them, one thread per query row, so the sets work
     // out of step and neither waits for the other until the end, where their (m, l, O) join
@@ -287,7 +296,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
     // stay exact: every term of a row is relative to the same stale maximum).
     constexpr float RESCALE_AT = 8.0f;
     const int quarter = warp & 3;
-    const int set = (warp - 2) >> 2;
+    const int set = (warp - SOFTMAX_WARP0) >> 2;
     const int row = quarter * 32 + lane;
     const uint32_t lane_off = (uint32_t)(quarter * 32) << 16;
     const int my_pos = pos0 + row;
