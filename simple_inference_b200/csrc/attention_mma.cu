@@ -19,7 +19,9 @@
 //   attn_decode_tma_kernel  the same, for head sizes that are multiples of 64 and pages
 //                        of 8 to 64 tokens: keys and values arrive as TMA boxes
 //                        (cp.async.bulk.tensor, 128-byte swizzle) announced by
-//                        mbarriers, and no thread computes an address.
+//                        mbarriers, and no thread computes an address.  A fifth warp
+//                        looks the pages up and issues the copies, so the four computing
+//                        warps never stand behind a table read or a copy's issue.
 //
 // Both compute S = (Q K^T) * scale with mma.sync m16n8k16 (bf16 in, float32
 // accumulate), mask by absolute position (key j visible to a query at position
@@ -546,7 +548,10 @@ __device__ __forceinline__ void pv_tile_sw(float (&o)[D / 8][4], const float (&s
   }
 }
 
-__global__ void __launch_bounds__(THREADS)
+constexpr int DECODE_TMA_THREADS = THREADS + 32;  // four computing warps and a producer warp
+__device__ __forceinline__ void compute_warps_sync() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+__global__ void __launch_bounds__(DECODE_TMA_THREADS)
 attn_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, const bf16* __restrict__ q,
                        int q_stride, const int* __restrict__ block_table, int table_stride,
                        const int* __restrict__ cu_q, const int* __restrict__ positions,
@@ -613,13 +618,13 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, const bf16*
                          (t == tile_first && k_lo_all % KV_TILE != 0);
     if (partial) {
       uint4* z = reinterpret_cast<uint4*>(stages_ptr + st * TMA_STAGE_BYTES);
-      for (int i = tid; i < TMA_STAGE_BYTES / 16; i += THREADS) z[i] = make_uint4(0, 0, 0, 0);
+      for (int i = tid; i < TMA_STAGE_BYTES / 16; i += DECODE_TMA_THREADS) z[i] = make_uint4(0, 0, 0, 0);
     }
   }
   fence_proxy_async_smem();
   __syncthreads();  // barriers initialised, stages zeroed
 
-  // Warp 0 issues the boxes of tile number `i` of this block into stage i % TMA_STAGES: lane pg
+  // Warp 4 issues the boxes of tile number `i` of this block into stage i % TMA_STAGES: lane pg
   // looks up and fetches page pg of the tile, so a tile's table reads are in flight together
   // and the next tile's are under way while this one is computed.
   const int pages_per_tile = KV_TILE / page_size;
@@ -645,27 +650,36 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, const bf16*
       }
     }
   };
-  int page_next = -1;
-  int first[TMA_STAGES];
-  if (warp == 0) {
-#pragma unroll
-    for (int i = 0; i < TMA_STAGES; ++i) first[i] = lookup(i);
-#pragma unroll
-    for (int i = 0; i < TMA_STAGES - 1; ++i)
-      if (i < n_my && tile_a + i != tile_end - 1) issue(i, first[i]);  // old keys: no need to wait
-    page_next = first[TMA_STAGES - 1];
+  if (warp == 4) {
+    // The producer warp.  A tile below the current position holds keys of earlier steps and is
+    // fetched at once; only the tile that holds the current position (whose key and value the
+    // kernel before this one writes) waits for that kernel.
+    bool waited = false;
+    int page = lookup(0);
+    for (int nx = 0; nx < n_my; ++nx) {
+      const int page_after = lookup(nx + 1);  // under way while this tile is issued
+      const int nst = nx % TMA_STAGES;
+      const uint32_t nuse = (uint32_t)(nx / TMA_STAGES);
+      if (tile_a + nx == tile_end - 1 && !waited) {
+        pdl_wait();
+        waited = true;
+      }
+      const bool free_now = nuse == 0 || mbar_wait_bounded(empty0 + 8 * nst, (nuse - 1) & 1u);
+      if (!__all_sync(0xffffffffu, free_now)) {
+        if (lane == 0) atomicExch(&failed, 1);
+        break;
+      }
+      issue(nx, page);
+      page = page_after;
+    }
+    return;
   }
   pdl_wait();
-  if (warp == 0) {
-#pragma unroll
-    for (int i = 0; i < TMA_STAGES - 1; ++i)
-      if (i < n_my && tile_a + i == tile_end - 1) issue(i, first[i]);
-  }
   // Q rows by cp.async: one per query head of the chunk, the rest zero
   if (n_my > 0) load_q_rows(sQ, q + (long long)tok * q_stride + (long long)head0 * D, D, n_heads_here, 16);
   cp_async_commit();
   cp_async_wait<0>();
-  __syncthreads();  // Q in place
+  compute_warps_sync();  // Q in place
 
   float o[D / 8][4];
 #pragma unroll
@@ -678,18 +692,6 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, const bf16*
   for (int i = 0; i < n_my && ok; ++i) {
     const int st = i % TMA_STAGES;
     const uint32_t use = (uint32_t)(i / TMA_STAGES);  // how often this stage was used before
-    if (warp == 0) {  // refill the stage that tile i-1 used, once all four warps have left it
-      const int nx = i + TMA_STAGES - 1;
-      if (nx < n_my) {
-        const int nst = nx % TMA_STAGES;
-        const uint32_t nuse = (uint32_t)(nx / TMA_STAGES);
-        const bool free_now = nuse == 0 || mbar_wait_bounded(empty0 + 8 * nst, (nuse - 1) & 1u);
-        if (__all_sync(0xffffffffu, free_now)) issue(nx, page_next);
-        else if (lane == 0) atomicExch(&failed, 1);
-        page_next = lookup(nx + 1);
-      }
-    }
-    __syncwarp();
     if (!mbar_wait_bounded(full0 + 8 * st, use & 1u)) {
       atomicExch(&failed, 1);
       ok = false;
@@ -715,7 +717,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, const bf16*
     __syncwarp();
     if (lane == 0) mbar_arrive(empty0 + 8 * st);
   }
-  __syncthreads();  // every warp has left the stages: the space is reused for the merge
+  compute_warps_sync();  // every warp has left the stages: the space is reused for the merge
   const bool bad = failed != 0;
 
   float* wm = reinterpret_cast<float*>(stages_ptr);
@@ -738,7 +740,7 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, const bf16*
       dst[1] = o[dt][2 * r + 1];
     }
   }
-  __syncthreads();
+  compute_warps_sync();
   for (int idx = tid; idx < n_heads_here * D; idx += THREADS) {
     const int row = idx / D, d = idx - row * D;
     float mm = -INFINITY;
@@ -892,7 +894,7 @@ SI_API int si_attn_decode(const void* q, int q_stride, const void* pool, int n_p
       if (e != cudaSuccess) return (int)e;
       tma_configured = true;
     }
-    SI_LAUNCH(si::attn_decode_tma_kernel, grid, si::THREADS, si::DECODE_TMA_SMEM, stream, pool_map,
+    SI_LAUNCH(si::attn_decode_tma_kernel, grid, si::DECODE_TMA_THREADS, si::DECODE_TMA_SMEM, stream, pool_map,
               (const si::bf16*)q, q_stride, block_table, table_stride, cu_q, positions, single_seqs,
               (si::bf16*)out, out_stride, part_acc, part_ml, n_q_heads, n_kv_heads, page_size,
               scale * si::LOG2E, window, n_splits);
