@@ -329,12 +329,14 @@ def main() -> int:
                           "layers": cfg.num_hidden_layers, "ms": round(pre_ms, 3)}))
         return 0
 
+    # the prefill is one step of some 12 ms, timed alone like the burst product its fraction is taken
+    # of: it runs before the seconds of decoding that bring the GPU to its power cap
+    pre_ms = time_prefill(model, cfg)
     ms, launches, ctx_mean, clocks = time_decode(model, cfg, args.batch, args.steps, warmup, True)
     step_bytes = weight_bytes + args.batch * ctx_mean * kv_bytes_per_token(cfg)
     achieved = step_bytes / (ms * 1e-3) / 1e9
     e2e_ms, h2d, d2h = time_e2e(model, cfg, args.batch, args.steps, warmup)
 
-    pre_ms = time_prefill(model, cfg)
     T, d = PREFILL_TOKENS, cfg.head_dim
     flops = 2 * T * layer_params + 2 * head_params \
         + cfg.num_hidden_layers * 2 * cfg.num_attention_heads * d * T * (T + 1)  # QK^T and PV, causal
