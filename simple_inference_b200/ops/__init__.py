@@ -373,7 +373,7 @@ MAX_KV_SPLITS = 32
 # part plus a part per 64-key tile, the blocks run in waves of as many as fit on the GPU
 # (3 per SM), and joining the splits costs a little more with each split.
 _RESIDENT_BLOCKS = 3 * 148
-_BLOCK_US, _TILE_US, _MERGE_US, _MERGE_SPLIT_US = 4.0, 1.17, 2.0, 0.1
+_BLOCK_US, _TILE_US, _MERGE_US, _MERGE_SPLIT_US = 6.0, 0.8, 2.0, 0.3
 
 
 @functools.lru_cache(maxsize=4096)
