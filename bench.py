@@ -11,9 +11,9 @@ prefill of 2,048 tokens, the decode roofline (weights + live cache bytes over
 the step time against the measured copy bandwidth) and decode at batch 1 and 64.
 This engine runs on one GPU: for N > 1 it says so and exits with 2.
 
-``--impl reference`` would run the unmodified reference from ``baseline/_ref``;
-the reference is a flat folder of modules without packaging metadata that pip
-refuses to install, so that arm prints its ``unavailable`` line.
+``--impl reference`` runs the unmodified reference from ``baseline/_ref`` on the
+same workload through its own engine (``baseline/reference_arm.py``, a process
+of its own) and prints the same line with ``"impl": "reference"``.
 """
 
 from __future__ import annotations
@@ -23,7 +23,6 @@ import json
 import os
 import subprocess
 import sys
-import threading
 import time
 from pathlib import Path
 
@@ -62,62 +61,7 @@ def peaks() -> tuple[dict, str]:
     return dict(FALLBACK_PEAKS), "fallback"
 
 
-class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while a region is timed."""
-
-    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
-              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-              "clocks_event_reasons.sw_power_cap")
-
-    def __init__(self):
-        self.samples: list[list[str]] = []
-        self.stamped: list[tuple[float, list[str]]] = []  # (arrival time, fields)
-        self.proc = None
-        self.t0 = self.t1 = None
-
-    def mark_start(self):
-        """The timed region starts now: samples from here on count (the tool needs a moment to
-        come up, so it is started before the warm-up and the region is marked)."""
-        self.t0 = time.time()
-
-    def mark_end(self):
-        self.t1 = time.time()
-
-    def __enter__(self):
-        try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "25"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
-            self.thread.start()
-        except OSError:
-            self.proc = None
-        return self
-
-    def _read(self):
-        for line in self.proc.stdout:
-            parts = [p.strip() for p in line.split(",")]
-            if len(parts) == 6:
-                self.stamped.append((time.time(), parts))
-
-    def __exit__(self, *exc):
-        if self.proc is not None:
-            self.proc.terminate()
-            try:
-                self.proc.wait(timeout=5)
-            except subprocess.TimeoutExpired:
-                self.proc.kill()
-
-    def summary(self) -> dict:
-        lo = self.t0 if self.t0 is not None else 0.0
-        hi = (self.t1 if self.t1 is not None else time.time()) + 0.03
-        self.samples = [p for t, p in self.stamped if lo <= t <= hi] or [p for _, p in self.stamped[-1:]]
-        mhz = sorted(int(s[0]) for s in self.samples if s[0].isdigit())
-        mx = [int(s[1]) for s in self.samples if s[1].isdigit()]
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        reasons = [n for i, n in enumerate(names) if any(s[2 + i] == "Active" for s in self.samples)]
-        return {"sm_mhz": mhz[len(mhz) // 2] if mhz else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": reasons, "samples": len(self.samples)}
+from baseline.clock_sampler import ClockSampler  # noqa: E402
 
 
 def matmul_params(cfg) -> tuple[int, int]:
@@ -176,11 +120,7 @@ def time_decode(model, cfg, batch, steps, warmup, sample_clocks=False):
 
     def one(i):
         logits = runner.step([StepEntry(b, [feed[i][b]], [0]) for b in range(batch)])
-        # sampling stays on the device here: no read-back inside the device-timed region
-        d = sampler._dev
-        ops.sample(logits, sampler._field(d, 0, batch).view(torch.float32), sampler._field(d, 1, batch),
-                   sampler._field(d, 2, batch).view(torch.float32), sampler._field(d, 3, batch),
-                   sampler._field(d, 4, batch), sampler._field(d, 5, batch), sampler._out[:batch])
+        sampler.sample_on_device(logits)  # no read-back inside the device-timed region
 
     sampler.sample(runner.step([StepEntry(b, [1], [0]) for b in range(batch)]), greedy)  # sets params
     clocks = ClockSampler() if sample_clocks else None
@@ -268,6 +208,32 @@ def time_prefill(model, cfg, reps=5):
     return sorted(times[2:])[len(times[2:]) // 2]
 
 
+def run_reference(args) -> int:
+    """Run ``baseline/reference_arm.py`` in a process of its own (so that nothing of this
+    package is imported beside the reference) and pass its JSON line on."""
+    cmd = [sys.executable, str(ROOT / "baseline" / "reference_arm.py"), "--steps", str(args.steps),
+           "--warmup", str(args.warmup), "--batch", str(args.batch)]
+    if args.no_points:
+        cmd.append("--no-points")
+    env = dict(os.environ)
+    env.pop("PYTHONPATH", None)
+    try:
+        proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True,
+                              env=env, cwd=str(ROOT / "baseline"), timeout=1500)
+    except subprocess.TimeoutExpired:
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference arm did not finish within 25 minutes"}))
+        return 0
+    lines = [ln for ln in proc.stdout.splitlines() if ln.startswith("{")]
+    if lines:
+        print(lines[-1])
+        return 0
+    tail = " ".join(proc.stderr.strip().splitlines()[-3:])[:500]
+    print(json.dumps({"impl": "reference", "unavailable":
+                      f"the reference arm exited with {proc.returncode}: {tail}"}))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -293,11 +259,11 @@ def main() -> int:
         MAX_CONTEXT = max(MAX_CONTEXT, DECODE_CONTEXT + 2048, PREFILL_TOKENS)
 
     if args.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "pip cannot install the reference offline: it is a flat folder of modules "
-                          "with no package metadata (setuptools: multiple top-level packages), so "
-                          "baseline/_ref is empty"}))
-        return 0
+        if args.gpus != 1:
+            print(json.dumps({"impl": "reference", "unavailable":
+                              "the reference engine runs on one GPU"}))
+            return 0
+        return run_reference(args)
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not built")
         return 2

@@ -62,7 +62,9 @@ class RopeScaling:
         }
 
 
-_DTYPE_NAMES = ("bfloat16", "float32")
+# dtypes a checkpoint may be stored in (reference ``config.py:137-142``); a float16
+# checkpoint is converted when it is loaded and served in bfloat16
+_DTYPE_NAMES = ("bfloat16", "float16", "float32")
 
 
 @dataclass(kw_only=True)

@@ -826,14 +826,7 @@ SI_API int si_attn_prefill(const void* q, int q_stride, const void* pool, const 
     return SI_ERR_ARG;
   if (n_q_heads > 65535) return SI_ERR_TOO_LARGE;
   if (n_tiles == 0) return SI_OK;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(si::attn_prefill_kernel,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)si::PREFILL_SMEM);
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
-  }
+  SI_ALLOW_DYNAMIC_SMEM((si::attn_prefill_kernel), (int)si::PREFILL_SMEM);
   dim3 grid(n_tiles, n_q_heads);
   SI_LAUNCH(si::attn_prefill_kernel, grid, si::THREADS, si::PREFILL_SMEM, stream,
       (const si::bf16*)q, q_stride, (const si::bf16*)pool, block_table, table_stride, cu_q,
@@ -867,14 +860,7 @@ SI_API int si_attn_decode(const void* q, int q_stride, const void* pool, int n_p
   const int grid_y = n_kv_heads * ((group + 15) / 16);
   if (grid_y > 65535 || n_splits > 65535 || n_q_heads > 65535) return SI_ERR_TOO_LARGE;
   if (n_single == 0) return SI_OK;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(si::attn_decode_kernel,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                         (int)si::DECODE_SMEM);
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
-  }
+  SI_ALLOW_DYNAMIC_SMEM((si::attn_decode_kernel), (int)si::DECODE_SMEM);
   float* part_acc = scratch;
   float* part_ml = scratch ? scratch + (long long)n_single * n_q_heads * n_splits * si::D : nullptr;
   dim3 grid(n_single, grid_y, n_splits);
@@ -886,14 +872,7 @@ SI_API int si_attn_decode(const void* q, int q_stride, const void* pool, int n_p
   if (tma_shapes &&
       si::make_bf16_map(&pool_map, pool, (long long)n_pages * 2 * n_kv_heads * page_size, si::D,
                         si::D, page_size)) {
-    static bool tma_configured = false;
-    if (!tma_configured) {
-      cudaError_t e = cudaFuncSetAttribute(si::attn_decode_tma_kernel,
-                                           cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                           (int)si::DECODE_TMA_SMEM);
-      if (e != cudaSuccess) return (int)e;
-      tma_configured = true;
-    }
+    SI_ALLOW_DYNAMIC_SMEM((si::attn_decode_tma_kernel), (int)si::DECODE_TMA_SMEM);
     SI_LAUNCH(si::attn_decode_tma_kernel, grid, si::DECODE_TMA_THREADS, si::DECODE_TMA_SMEM, stream, pool_map,
               (const si::bf16*)q, q_stride, block_table, table_stride, cu_q, positions, single_seqs,
               (si::bf16*)out, out_stride, part_acc, part_ml, n_q_heads, n_kv_heads, page_size,
@@ -938,6 +917,9 @@ SI_API int si_attn_decode_static(const void* q, int q_stride, const void* pool, 
                                  int page_size, float scale, int window, int n_splits,
                                  cudaStream_t stream) {
   if (n_single < 0 || n_q_heads <= 0 || n_splits < 1) return SI_ERR_ARG;
+  // each factor is bounded before the product is formed, so the product cannot wrap
+  if (n_splits > 65535 || n_q_heads > 65535 || n_single > SI_ATTN_STATIC_SCRATCH_FLOATS)
+    return SI_ERR_TOO_LARGE;
   if (si_attn_decode_scratch_floats(n_single, n_q_heads, n_splits) > SI_ATTN_STATIC_SCRATCH_FLOATS)
     return SI_ERR_TOO_LARGE;
   int dev = -1;

@@ -471,13 +471,7 @@ SI_API int si_attn_prefill_tc(const void* q, int q_stride, int n_tokens, const v
   CUtensorMap q_map, kv_map;
   if (!make_bf16_map(&q_map, q, n_tokens, n_q_heads * HD, q_stride, TQ)) return SI_ERR_UNSUPPORTED;
   if (!make_page_map(&kv_map, pool, n_pages, n_kv_heads, page_size, HD, 1)) return SI_ERR_UNSUPPORTED;
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, ATC_SMEM);
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
-  }
+  SI_ALLOW_DYNAMIC_SMEM((attn_prefill_tc_kernel), ATC_SMEM);
   dim3 grid(n_q_heads, n_tiles);
   SI_LAUNCH(attn_prefill_tc_kernel, grid, ATC_THREADS, ATC_SMEM, stream, q_map, kv_map, block_table,
             table_stride, cu_q, positions, tile_seq, tile_start, (bf16*)out, out_stride, n_q_heads,

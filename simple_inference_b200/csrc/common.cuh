@@ -68,8 +68,7 @@ static inline cudaError_t launch(Kernel kernel, dim3 grid, dim3 block, size_t sm
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  static const bool serial = getenv("SI_B200_NO_PDL") != nullptr;  // plain stream order, for A/B timing
-  cfg.numAttrs = serial ? 0 : 1;
+  cfg.numAttrs = 1;
   return cudaLaunchKernelEx(&cfg, kernel, args...);
 }
 
@@ -77,6 +76,23 @@ static inline cudaError_t launch(Kernel kernel, dim3 grid, dim3 block, size_t sm
   do {                                                                                     \
     cudaError_t le__ = si::launch(kernel, dim3(grid), dim3(block), smem, stream, __VA_ARGS__); \
     if (le__ != cudaSuccess) return (int)le__;                                             \
+  } while (0)
+
+// Raise a kernel's dynamic shared memory limit, once per call site and device (the attribute
+// belongs to the device's copy of the kernel, so a second GPU needs its own call).
+#define SI_ALLOW_DYNAMIC_SMEM(kernel, bytes)                                                  \
+  do {                                                                                        \
+    static bool done__[64];                                                                   \
+    int dev__ = 0;                                                                            \
+    cudaError_t ae__ = cudaGetDevice(&dev__);                                                 \
+    if (ae__ != cudaSuccess) return (int)ae__;                                                \
+    if (dev__ < 0 || dev__ >= 64) return SI_ERR_TOO_LARGE;                                    \
+    if (!done__[dev__]) {                                                                     \
+      ae__ = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,        \
+                                  (int)(bytes));                                              \
+      if (ae__ != cudaSuccess) return (int)ae__;                                              \
+      done__[dev__] = true;                                                                   \
+    }                                                                                         \
   } while (0)
 
 // 8 consecutive elements as float, for 16-byte (bfloat16) or 32-byte (float32) vector access

@@ -33,10 +33,7 @@ namespace si {
 typedef __nv_bfloat16 bf16;
 constexpr int SK_THREADS = 256;
 constexpr int SK_WARPS = 8;
-#ifndef SI_SK_UNROLL
-#define SI_SK_UNROLL 4
-#endif
-constexpr int SK_UNROLL = SI_SK_UNROLL;
+constexpr int SK_UNROLL = 4;  // 32-wide k-steps a warp requests at a time
 
 enum SkinnyEpilogue { SK_BF16 = 0, SK_F32 = 1, SK_SWIGLU = 2, SK_ROPE = 3 };
 

@@ -271,13 +271,7 @@ static int choose_bn(int M, int N, int n_sms) {
 template <int EPI, int BN>
 static int launch_tc(const CUtensorMap& map_x, const CUtensorMap& map_w, bf16* out, int ldo, int M,
                      int N, int K, int up_row0, int* status, int n_sms, cudaStream_t stream) {
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<EPI, BN>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES);
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
-  }
+  SI_ALLOW_DYNAMIC_SMEM((gemm_tc_kernel<EPI, BN>), TC_SMEM_BYTES);
   constexpr int tile_n = EPI == TC_EPI_SWIGLU ? BN / 2 : BN;
   const int n_tiles = ((M + TC_BM - 1) / TC_BM) * ((N + tile_n - 1) / tile_n);
   const int grid = n_tiles < n_sms ? n_tiles : n_sms;

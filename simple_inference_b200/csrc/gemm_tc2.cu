@@ -317,13 +317,7 @@ static int choose_bn2(int M, int N, int n_pairs) {
 template <int EPI, int BN>
 static int launch_tc2(const CUtensorMap& map_x, const CUtensorMap& map_w, bf16* out, int ldo, int M,
                       int N, int K, int up_row0, int* status, int n_sms, cudaStream_t stream) {
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc2_kernel<EPI, BN>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, T2_SMEM_BYTES);
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
-  }
+  SI_ALLOW_DYNAMIC_SMEM((gemm_tc2_kernel<EPI, BN>), T2_SMEM_BYTES);
   constexpr int tile_n = EPI == T2_EPI_SWIGLU ? BN / 2 : BN;
   const int n_tiles = ((M + 2 * T2_BM - 1) / (2 * T2_BM)) * ((N + tile_n - 1) / tile_n);
   int pairs = n_sms / 2;
@@ -341,8 +335,7 @@ static int launch_tc2(const CUtensorMap& map_x, const CUtensorMap& map_w, bf16* 
   attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  static const bool serial = getenv("SI_B200_NO_PDL") != nullptr;
-  cfg.numAttrs = serial ? 1 : 2;
+  cfg.numAttrs = 2;
   cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<EPI, BN>, map_x, map_w, out, ldo, M, N, K,
                                      up_row0, status);
   return e == cudaSuccess ? SI_OK : (int)e;

@@ -13,7 +13,9 @@
 // torch.multinomial on the global generator, which depends on batch order.
 // Here token = argmax_v (z_v + G_v) with Gumbel noise G_v = -log(-log(u_v)) and
 // u_v a hash of (seed, stream, counter, v): a request's draw is the same alone
-// or in any batch.  Thresholds are found by bitwise search over the ordered
+// or in any batch.  A row without one comparable logit (all NaN, which is how a
+// failed kernel upstream marks its output) yields token -1, never an index.
+// Thresholds are found by bitwise search over the ordered
 // integer image of the floats (no sort, no scratch memory).
 #include "common.cuh"
 
@@ -30,10 +32,12 @@ __device__ __forceinline__ uint32_t mix32(uint32_t x) {
   return x;
 }
 
-// uniform in (0,1) for (seed, stream, counter, v)
+// uniform strictly inside (0,1) for (seed, stream, counter, v): 23 bits of the hash plus a
+// half, which float32 holds exactly (24 bits would round 16777215.5 up to 2^24, u = 1 and
+// infinite Gumbel noise)
 __device__ __forceinline__ float uniform01(uint32_t base, uint32_t v) {
   const uint32_t h = mix32(base ^ mix32(v + 0x9e3779b9U));
-  return ((float)(h >> 8) + 0.5f) * (1.0f / 16777216.0f);
+  return ((float)(h >> 9) + 0.5f) * (1.0f / 8388608.0f);
 }
 
 __device__ __forceinline__ uint32_t ordered_key(float f) {
@@ -100,7 +104,7 @@ sample_kernel(const float* __restrict__ logits, int vocab, int ld,
     ArgBest b{-INFINITY, 0x7fffffff};
     for (int v = tid; v < vocab; v += SAMPLE_THREADS) b = better(b, ArgBest{row[v], v});
     b = block_argbest(b, sv, sidx);
-    if (tid == 0) out[r] = b.i;
+    if (tid == 0) out[r] = (b.i == 0x7fffffff) ? -1 : b.i;  // -1: no comparable logit (NaN row)
     return;
   }
 
@@ -169,7 +173,7 @@ sample_kernel(const float* __restrict__ logits, int vocab, int ld,
     b = better(b, ArgBest{z + g, v});
   }
   b = block_argbest(b, sv, sidx);
-  if (tid == 0) out[r] = b.i;
+  if (tid == 0) out[r] = (b.i == 0x7fffffff) ? -1 : b.i;
 }
 
 }  // namespace si

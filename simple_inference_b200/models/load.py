@@ -11,7 +11,7 @@ from ..config.model_config import ModelConfig
 from ..config.registry import architecture_of, read_config
 from ..parts.base import Runtime
 from ..weights.loader import load_tensors
-from ..weights.random_init import random_tensors
+from ..weights.random_init import _STORE_DTYPES, random_tensors
 from .plan import DecoderModel
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16,
@@ -46,6 +46,6 @@ def random_model(config: dict[str, Any], seed: int, dtype: str | torch.dtype = "
     arch = architecture_of(config)
     cfg = arch.config_class.from_dict(config)
     model = DecoderModel(arch.plan(cfg))
-    store = _DTYPES[getattr(cfg, "torch_dtype", "bfloat16")]
+    store = _STORE_DTYPES[getattr(cfg, "torch_dtype", "bfloat16")]
     model.bind(random_tensors(model.tensor_specs(), seed, rt, store), rt)
     return cfg, model

@@ -5,17 +5,19 @@ compiled library on the current CUDA stream.  There is no other implementation
 behind these names: a tensor that is not on a CUDA device, or a library that
 cannot be built, raises.
 
-bfloat16 matrix products call the library GEMM (cuBLAS through ``torch.mm``),
-as the reference's engine does for every linear layer (``F.linear``,
-``ops/attention.py:128-130``, ``ops/mlp.py:117,128``, ``ops/embedding.py:92``);
-float32 products run the hand-written FMA kernel, never a tensor-core mode.
+bfloat16 matrix products run hand-written kernels: a weight-streaming product
+for the few rows of a decode step and tcgen05 products (one SM or a pair of SMs
+per tile) for prompt portions; only the row counts between them call the library
+GEMM (cuBLAS through ``torch.mm``), which the reference's engine calls for every
+linear layer (``F.linear``, ``ops/attention.py:128-130``, ``ops/mlp.py:117,128``,
+``ops/embedding.py:92``).  float32 products run the hand-written FMA kernel, never
+a tensor-core mode.
 """
 
 from __future__ import annotations
 
 import ctypes
 import functools
-import os
 
 import torch
 
@@ -213,7 +215,7 @@ def linear_tc(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, swiglu: 
             or out.stride(0) % 8 != 0 or out.data_ptr() % 16 != 0:
         raise KernelError("linear_tc: operands do not fit")
     if paired is None:
-        paired = m >= PAIRED_MIN_ROWS and not os.environ.get("SI_B200_TC_UNPAIRED")
+        paired = m >= PAIRED_MIN_ROWS
     fn = core().si_gemm_tc2_bf16 if paired else core().si_gemm_tc_bf16
     _check(fn(_p(x), x.stride(0), _p(weight), _p(out), out.stride(0), m, n, k,
               2 if swiglu else 0, _p(status_tensor(x.device)), _stream()),

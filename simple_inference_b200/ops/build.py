@@ -99,12 +99,8 @@ def _run(cmd: list[str], what: str) -> None:
 
 
 def library_path(name: str, source_names: list[str], defines: list[str] | None = None) -> Path:
-    """Build (if needed) and return the shared library made from ``source_names``.
-
-    ``$SI_B200_NVCC_FLAGS`` adds compiler flags (a developer's knob for timing
-    variants of a kernel; the flags are part of the library's hash).
-    """
-    defines = list(defines or []) + os.environ.get("SI_B200_NVCC_FLAGS", "").split()
+    """Build (if needed) and return the shared library made from ``source_names``."""
+    defines = list(defines or [])
     sources = [CSRC / s for s in source_names]
     for s in sources:
         if not s.is_file():

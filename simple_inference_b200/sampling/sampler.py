@@ -53,10 +53,7 @@ class Sampler:
             u32[4 * m + i] = stream & 0xFFFFFFFF
             u32[5 * m + i] = counter & 0xFFFFFFFF
         self._dev.copy_(self._host, non_blocking=True)
-        d = self._dev
-        ops.sample(logits, self._field(d, 0, n).view(torch.float32), self._field(d, 1, n),
-                   self._field(d, 2, n).view(torch.float32), self._field(d, 3, n),
-                   self._field(d, 4, n), self._field(d, 5, n), self._out[:n])
+        self.sample_on_device(logits)
         self._out_host[:n].copy_(self._out[:n], non_blocking=True)
         if self.device.type == "cuda":
             # the kernels' status word rides home with the tokens: one synchronisation for both
@@ -65,4 +62,19 @@ class Sampler:
             torch.cuda.current_stream().synchronize()
             if int(self._status_host[0]) != 0:
                 ops.check_status(self.device)
-        return self._out_host[:n].tolist()
+        tokens = self._out_host[:n].tolist()
+        if min(tokens) < 0:
+            bad = [i for i, t in enumerate(tokens) if t < 0]
+            raise ops.KernelError(f"sampling: rows {bad} of the logits hold no comparable value "
+                                  f"(NaN): a kernel of this step failed")
+        return tokens
+
+    def sample_on_device(self, logits: torch.Tensor) -> torch.Tensor:
+        """Draw for the rows of ``logits`` with the options of the last ``sample`` call already
+        on the device; the tokens stay on the device (no copy, no synchronisation)."""
+        n = logits.shape[0]
+        d = self._dev
+        ops.sample(logits, self._field(d, 0, n).view(torch.float32), self._field(d, 1, n),
+                   self._field(d, 2, n).view(torch.float32), self._field(d, 3, n),
+                   self._field(d, 4, n), self._field(d, 5, n), self._out[:n])
+        return self._out[:n]

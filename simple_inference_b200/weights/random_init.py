@@ -26,7 +26,7 @@ from ..config.registry import architecture_of
 from ..parts.base import Runtime, TensorSpec
 from .loader import target_dtype
 
-_STORE_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
+_STORE_DTYPES = {"bfloat16": torch.bfloat16, "float16": torch.float16, "float32": torch.float32}
 
 
 def _tensor_seed(seed: int, name: str) -> int:

@@ -193,6 +193,13 @@ def _mix32(x):
     return x
 
 
+def uniform_from_hash(h):
+    """float32 uniform strictly inside (0, 1) from 32-bit hashes: 23 bits plus a half."""
+    import numpy as np
+    return ((h.astype(np.uint64) >> np.uint64(9)).astype(np.float32) + np.float32(0.5)) \
+        * np.float32(1.0 / 8388608.0)
+
+
 def gumbel_noise(seed, stream, counter, vocab):
     """float32 Gumbel noise per vocabulary entry from a counter-based hash."""
     import numpy as np
@@ -209,7 +216,7 @@ def gumbel_noise(seed, stream, counter, vocab):
         return x
 
     h = mix(np.uint64(base) ^ mix(v + np.uint64(0x9E3779B9)))
-    u = ((h >> np.uint64(8)).astype(np.float32) + np.float32(0.5)) * np.float32(1.0 / 16777216.0)
+    u = uniform_from_hash(h)
     return torch.from_numpy(-np.log(-np.log(u, dtype=np.float32), dtype=np.float32))
 
 

@@ -42,7 +42,7 @@ def test_missing_keys_are_all_listed():
     {"head_dim": 15},                      # odd head size
     {"rms_norm_eps": 0.0},
     {"vocab_size": -1},
-    {"torch_dtype": "float16"},
+    {"torch_dtype": "float8"},
     {"hidden_act": "gelu"},
     {"attention_bias": True},
     {"rope_scaling": {"rope_type": "llama3", "factor": 8.0}},   # llama3 keys missing
@@ -79,3 +79,8 @@ def test_plan_carries_only_config_values():
         assert mixer["position"].params["theta"] == c.rope_theta
         assert plan.layers[0].block.params["mixer_norm"].params["eps"] == c.rms_norm_eps
         assert plan.tie_embeddings == c.tie_word_embeddings
+
+
+def test_float16_checkpoints_are_accepted():
+    # reference config.py:137-142 maps bfloat16, float16 and float32
+    assert LlamaConfig.from_dict({**TINY_A, "torch_dtype": "float16"}).torch_dtype == "float16"

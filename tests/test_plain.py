@@ -101,3 +101,18 @@ def test_sampling_rules():
     for c in range(3000):
         counts[plain_llama.sample(small, 1.0, seed=9, counter=c)] += 1
     assert (counts / 3000 - torch.softmax(small, -1)).abs().max() < 0.03
+
+
+def test_uniform_of_every_hash_lies_strictly_inside_the_unit_interval():
+    """The Gumbel draw takes -log(-log(u)): u = 0 or u = 1 would give infinite noise and make
+    its token win (or lose) whatever its logit.  The uniform keeps 23 bits of the hash; sweep
+    all of them, with the dropped low bits both clear and set."""
+    import numpy as np
+    top = np.arange(1 << 23, dtype=np.uint64) << np.uint64(9)
+    for low in (0, 0x1FF):
+        u = plain_llama.uniform_from_hash(top | np.uint64(low))
+        assert u.dtype == np.float32
+        assert float(u.min()) > 0.0 and float(u.max()) < 1.0
+        noise = -np.log(-np.log(u, dtype=np.float32), dtype=np.float32)
+        assert np.isfinite(noise).all()
+    assert np.isfinite(plain_llama.gumbel_noise(3, 1, 2, 200_000).numpy()).all()

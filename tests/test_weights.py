@@ -105,3 +105,15 @@ def test_missing_files(tmp_path):
     _, specs, opt = _specs(TINY_A)
     with pytest.raises(FileNotFoundError):
         load_tensors(tmp_path, specs, opt, runtime_for("bfloat16", "cpu"))
+
+
+def test_a_float16_checkpoint_loads_and_is_served_in_bfloat16(tmp_path):
+    """torch_dtype "float16" (reference config.py:137-142): tensors are converted as they load."""
+    write_random_model(tmp_path, {**TINY_A, "torch_dtype": "float16"}, 1)
+    stored = load_file(str(tmp_path / "model.safetensors"))
+    assert all(t.dtype == torch.float16 for t in stored.values())
+    _, specs, opt = _specs(TINY_A)
+    bf = load_tensors(tmp_path, specs, opt, runtime_for("bfloat16", "cpu"))
+    assert all(t.dtype == torch.bfloat16 for t in bf.values())
+    name = "model.layers.0.mlp.up_proj.weight"
+    assert torch.equal(bf[name], stored[name].to(torch.bfloat16))

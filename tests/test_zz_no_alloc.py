@@ -79,8 +79,8 @@ def test_static_scratch_entry_point_matches_the_ordinary_one(d):
         assert _call(lib, "si_attn_decode_static", c, got, splits) == 0
         torch.cuda.synchronize()
         assert torch.cuda.memory_allocated() == held   # no scratch came from torch either
-        # same kernels, same order of sums: the tolerance of the other attention tests
-        assert (got.float() - want.float()).abs().max() < 2e-2
+        # same kernels, same split count, same order of sums: bit for bit
+        assert torch.equal(got, want)
         # and against plain float32 attention over the same pages
         from tests import twin_ops
         ref = torch.zeros(c["n"], c["hq"] * d, device="cuda")
@@ -99,6 +99,13 @@ def test_static_scratch_entry_point_refuses_what_does_not_fit():
     assert _call(lib, "si_attn_decode_static", c, out, 32) == -4     # SI_ERR_TOO_LARGE
     torch.cuda.synchronize()
     assert float(out.float().min()) == 5.0                           # nothing ran
+    # absurd sizes are refused by their ranges, before any product of them is formed
+    huge = dict(c, n=2**31 - 1, hq=65535)
+    assert _call(lib, "si_attn_decode_static", huge, out, 65535) == -4
+    assert _call(lib, "si_attn_decode_static", dict(c, hq=65536 * 8, hkv=8), out, 2) == -4
+    assert _call(lib, "si_attn_decode_static", c, out, 70000) == -4
+    torch.cuda.synchronize()
+    assert float(out.float().min()) == 5.0
     assert _call(lib, "si_attn_decode_static", c, out, 2) == 0       # the same batch with fewer splits fits
     torch.cuda.synchronize()
     assert float(out.float().abs().max()) < 5.0
