@@ -147,9 +147,32 @@ def time_decode(model, cfg, batch, steps, warmup, sample_clocks=False):
     ms = start.elapsed_time(end) / steps
     launches = (ops.launch_count - k0) + (runner.replayed_kernels - r0)
     ctx_mean = DECODE_CONTEXT + 1 + warmup + (steps - 1) / 2
+    check = check_against_eager(runner, cache, batch, feed[0]) if not EAGER else None
     del runner, cache
     torch.cuda.empty_cache()
-    return ms, launches, ctx_mean, (clocks.summary() if clocks else None)
+    return ms, launches, ctx_mean, (clocks.summary() if clocks else None), check
+
+
+def check_against_eager(runner, cache, batch, tokens):
+    """Outside the timed region: one more step replayed from the graph, then the same tokens at
+    the same positions run eagerly (their keys and values land in the same slots again), and the
+    two sets of logits compared, as the reference's benchmark compares its decode backends
+    (``benchmarks/bench_paged_cudagraph.py:239-261``).  A graph that replayed stale sizes or
+    addresses would show here."""
+    import torch
+    from simple_inference_b200.engine import StepEntry
+    entries = [StepEntry(b, [tokens[b]], [0]) for b in range(batch)]
+    replayed = runner.step(entries).clone()
+    starts = [cache.length(b) - 1 for b in range(batch)]
+    ctx = runner.builder.build(entries, starts, runner.ws)
+    eager = runner.model.forward(ctx, runner.layer_caches)
+    torch.cuda.synchronize()
+    diff = float((replayed - eager).abs().max())
+    agree = float((replayed.argmax(-1) == eager.argmax(-1)).float().mean())
+    spread = float(eager.std())
+    ok = bool(torch.isfinite(replayed).all()) and diff < 0.25 * spread and agree >= 0.75
+    return {"max_abs_logit_diff": round(diff, 5), "top1_agree": round(agree, 4),
+            "logit_std": round(spread, 4), "ok": ok}
 
 
 def time_e2e(model, cfg, batch, steps, warmup):
@@ -168,13 +191,15 @@ def time_e2e(model, cfg, batch, steps, warmup):
     for _ in range(warmup):
         eng.step()
     torch.cuda.synchronize()
+    sent0 = eng.runner.builder.words_sent
     t0 = time.perf_counter()
     for _ in range(steps):
         out = eng.step()
         assert len(out) == batch
     torch.cuda.synchronize()
     dt = (time.perf_counter() - t0) / steps
-    h2d = eng.runner.builder.total * 4 + eng.sampler._host.numel() * 4
+    # the step's description (counted by the builder as it copies) and the sampling options
+    h2d = (eng.runner.builder.words_sent - sent0) * 4 // steps + eng.sampler.host_bytes
     d2h = batch * 4
     eng.reset()
     del eng
@@ -284,7 +309,7 @@ def main() -> int:
     weight_bytes = 2 * (layer_params + head_params)
 
     if args.only == "decode":
-        ms, launches, _, _ = time_decode(model, cfg, args.batch, args.steps, args.warmup)
+        ms, launches, _, _, _ = time_decode(model, cfg, args.batch, args.steps, args.warmup)
         print(json.dumps({"only": "decode", "batch": args.batch, "context": DECODE_CONTEXT,
                           "layers": cfg.num_hidden_layers, "eager": EAGER,
                           "ms_per_step": round(ms, 4), "launches": launches}))
@@ -298,7 +323,8 @@ def main() -> int:
     # the prefill is one step of some 12 ms, timed alone like the burst product its fraction is taken
     # of: it runs before the seconds of decoding that bring the GPU to its power cap
     pre_ms = time_prefill(model, cfg)
-    ms, launches, ctx_mean, clocks = time_decode(model, cfg, args.batch, args.steps, warmup, True)
+    ms, launches, ctx_mean, clocks, check = time_decode(model, cfg, args.batch, args.steps, warmup, True)
+    graph_check = {f"b{args.batch}": check}
     step_bytes = weight_bytes + args.batch * ctx_mean * kv_bytes_per_token(cfg)
     achieved = step_bytes / (ms * 1e-3) / 1e9
     e2e_ms, h2d, d2h = time_e2e(model, cfg, args.batch, args.steps, warmup)
@@ -311,8 +337,9 @@ def main() -> int:
     points = {}
     if not args.no_points:
         for b in (1, 64):
-            pms, _, _, _ = time_decode(model, cfg, b, max(10, args.steps // 2), warmup)
+            pms, _, _, _, check = time_decode(model, cfg, b, max(10, args.steps // 2), warmup)
             points[f"decode_b{b}"] = round(b / (pms * 1e-3), 1)
+            graph_check[f"b{b}"] = check
 
     line = {
         "metric": "decode tok/s, Llama 3.2 3B shape, batch 8, context 2048 (1 GPU)",
@@ -341,9 +368,13 @@ def main() -> int:
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"],
                      "unit": "GB/s", "frac": round(achieved / pk["hbm_gbs"], 4)},
         "points": points,
+        "graph_check": graph_check,
         "clocks": clocks,
     }
     print(json.dumps(line))
+    if not all(c["ok"] for c in graph_check.values()):
+        print("bench.py: a decode graph's logits part from the eager step's", file=sys.stderr)
+        return 3
     return 0
 
 

@@ -1,11 +1,13 @@
 """Cache manager: paged keys/values per layer group, block tables, state slots.
 
-Layers whose mixers need the same kind of cache form a *group*: same number of
-key/value heads, head size and window.  A group has its own pool of pages
-``[entries, pages+1, 2, kv_heads, page_size, head_dim]`` (one page id addresses
-the same slot in every cache entry of the group; the last page is scratch for
-padding rows of a fixed-size batch), its own allocator and, for every live
-request, its own block table.  A group that keeps every key holds a request's
+Layers whose mixers need the same kind of cache (equal cache specs: for keys and
+values the same number of heads, head size and window) form a *group*.  A group has
+its own pool of pages ``[entries, pages+1, *spec.page_shape(page_size)]`` (for keys
+and values ``[entries, pages+1, 2, kv_heads, page_size, head_dim]``; one page id
+addresses the same slot in every cache entry of the group; the last page is scratch
+for padding rows of a fixed-size batch), its own page size if the spec names one, its
+own allocator and, for every live request, its own block table.  The manager only
+counts pages: how a page is shaped is the spec's business.  A group that keeps every key holds a request's
 pages until the request ends; a group with a window gives a page back as soon
 as every key on it lies before the window of the request's next query.
 
@@ -24,11 +26,11 @@ from __future__ import annotations
 
 import heapq
 from dataclasses import dataclass, field
-from typing import Hashable
+from typing import Callable, Hashable
 
 import torch
 
-from ..parts.base import CacheSpec, LayerCache, PagedKVSpec, StateSpec
+from ..parts.base import CacheSpec, LayerCache
 from .allocator import OutOfPages, PageAllocator
 
 _STATE_DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16, "int32": torch.int32}
@@ -47,39 +49,49 @@ class _RequestPages:
 class PageGroup:
     """One layer group's pages."""
 
-    def __init__(self, index: int, spec: PagedKVSpec, entries: list[int], page_size: int,
+    def __init__(self, index: int, spec: CacheSpec, entries: list[int], page_size: int,
                  num_pages: int, dtype: torch.dtype, device: torch.device | None):
         self.index = index
         self.spec = spec
         self.entries = entries
-        self.page_size = page_size
+        self.page_size = page_size = int(getattr(spec, "page_size", None) or page_size)
+        self.page_shape = tuple(spec.page_shape(page_size))
+        self.window = getattr(spec, "window", None)
+        if callable(num_pages):
+            num_pages = int(num_pages(page_size))
         self.num_pages = num_pages
         self.scratch_page = num_pages
         self.allocator = PageAllocator(num_pages)
         self.requests: dict[Hashable, _RequestPages] = {}
         self.pool: torch.Tensor | None = None
         if device is not None:
-            self.pool = torch.zeros(
-                (len(entries), num_pages + 1, 2, spec.num_kv_heads, page_size, spec.head_dim),
-                dtype=dtype, device=device)
+            self.pool = torch.zeros((len(entries), num_pages + 1, *self.page_shape),
+                                    dtype=dtype, device=device)
 
     def pages_needed(self, total_tokens: int, max_step_tokens: int) -> int:
         """Most pages a request of ``total_tokens`` holds at any one time."""
         full = pages_for(total_tokens, self.page_size)
-        if self.spec.window is None:
+        if self.window is None:
             return full
-        live_keys = self.spec.window + max_step_tokens - 1
+        live_keys = self.window + max_step_tokens - 1
         return min(full, pages_for(live_keys, self.page_size) + 1)
 
     def bytes_per_page(self) -> int:
         elt = self.pool.element_size() if self.pool is not None else 2
-        return 2 * len(self.entries) * self.spec.num_kv_heads * self.page_size * self.spec.head_dim * elt
+        numel = 1
+        for n in self.page_shape:
+            numel *= n
+        return len(self.entries) * numel * elt
 
 
 class CacheManager:
-    def __init__(self, specs: list[CacheSpec | None], page_size: int, num_pages: int | dict[int, int],
+    def __init__(self, specs: list[CacheSpec | None], page_size: int,
+                 num_pages: "int | dict[int, int] | Callable[[int], int]",
                  max_requests: int, max_step_tokens: int, dtype: torch.dtype = torch.bfloat16,
                  device: torch.device | str | None = None):
+        """``page_size``: tokens per page for every group whose spec names no size of its own.
+        ``num_pages``: pages per group: one number for all, a number per group index, or a
+        function of the group's page size."""
         if page_size <= 0:
             raise ValueError(f"page_size must be positive, got {page_size}")
         if max_requests <= 0:
@@ -94,10 +106,15 @@ class CacheManager:
         # group cache entries by identical paged spec, in order of first appearance
         self.groups: list[PageGroup] = []
         self._entry_group: dict[int, tuple[int, int]] = {}  # entry -> (group, index in group)
-        by_spec: dict[PagedKVSpec, list[int]] = {}
+        by_spec: dict[CacheSpec, list[int]] = {}
         for e, spec in enumerate(self.specs):
-            if isinstance(spec, PagedKVSpec):
+            if spec is None:
+                continue
+            if spec.storage == "pages":
                 by_spec.setdefault(spec, []).append(e)
+            elif spec.storage != "slots":
+                raise ValueError(f"cache entry {e}: storage {spec.storage!r} is neither "
+                                 f"'pages' nor 'slots'")
         for gi, (spec, entries) in enumerate(by_spec.items()):
             n = num_pages[gi] if isinstance(num_pages, dict) else num_pages
             self.groups.append(PageGroup(gi, spec, entries, page_size, n, dtype, self.device))
@@ -108,8 +125,8 @@ class CacheManager:
         self.scratch_slot = max_requests
         self.state: dict[int, torch.Tensor] = {}
         for e, spec in enumerate(self.specs):
-            if isinstance(spec, StateSpec) and self.device is not None:
-                self.state[e] = torch.zeros((max_requests + 1, *spec.shape),
+            if spec is not None and spec.storage == "slots" and self.device is not None:
+                self.state[e] = torch.zeros((max_requests + 1, *spec.slot_shape()),
                                             dtype=_STATE_DTYPES[spec.dtype], device=self.device)
         self._free_slots: list[int] = list(range(max_requests))
         heapq.heapify(self._free_slots)
@@ -209,8 +226,8 @@ class CacheManager:
         end = start + new_tokens
         for g in self.groups:
             rp = g.requests[request]
-            if g.spec.window is not None:
-                first_needed_key = start - g.spec.window + 1
+            if g.window is not None:
+                first_needed_key = start - g.window + 1
                 keep_from = max(0, first_needed_key) // g.page_size
                 for lp in range(rp.first_live, min(keep_from, len(rp.table))):
                     if rp.table[lp] >= 0:
@@ -241,16 +258,16 @@ class CacheManager:
         """One view per cache entry, in entry order."""
         out: list[LayerCache | None] = []
         for e, spec in enumerate(self.specs):
-            if isinstance(spec, PagedKVSpec):
+            if spec is None:
+                out.append(None)
+            elif spec.storage == "pages":
                 gi, k = self._entry_group[e]
                 g = self.groups[gi]
                 out.append(LayerCache(spec, group=gi,
                                       pool=None if g.pool is None else g.pool[k],
                                       page_size=g.page_size))
-            elif isinstance(spec, StateSpec):
-                out.append(LayerCache(spec, state=self.state.get(e)))
             else:
-                out.append(None)
+                out.append(LayerCache(spec, state=self.state.get(e)))
         return out
 
     # ---------------------------------------------------------- accounting

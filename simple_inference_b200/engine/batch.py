@@ -4,35 +4,40 @@ A step gets a list of ``StepEntry``: for each request its next tokens (a
 portion of its prompt, or one decoded token) and the places among them whose
 logits are wanted.  All entries run as one batch of ``N`` tokens in ``S``
 sequences.  ``BatchBuilder`` lays the integers the kernels need into ONE pinned
-host buffer with a fixed layout and copies it to ONE device buffer per step;
-``StepContext`` holds views of that buffer:
+host buffer with a fixed layout, mirrored by ONE device buffer; ``StepContext``
+holds views of the device buffer:
 
-    token_ids[N] positions[N] tok_seq[N]      per token
-    kv_slots[g][N]                            per token and layer group: page*page_size+offset
     cu_q[S+1] seq_slots[S]                    per sequence: token range, state slot
-    block_tables[g][S, max_pages_g]           per sequence and layer group
+    token_ids[N] positions[N] tok_seq[N]      per token
     logit_rows[R]                             token indices whose logits are wanted
-    single_seqs[...] tile_seq[...] tile_start[...]   routing for the attention kernels:
-        sequences with exactly one token, and 64-token query tiles of the others
+    kv_slots[g][N]                            per token and layer group: page*page_size+offset
+    (a segment for every step planner of the model's parts, see parts/base.py)
+    block_tables[g][S, max_pages_g]           per sequence and layer group
 
-The layout is fixed by the capacities, so the same device addresses serve every
-step and every captured graph.  The reference rebuilds an int64 ``(B,
-max_blocks)`` table from Python lists and copies ids, positions and cos/sin
-rows separately each step (``serving/paged_decoder.py:207-257``).
+Everything but the block tables reaches the device in one copy per step; of the
+block tables only what changed since the last step is copied (the pages a request
+gained, or the rows of requests that moved), so a step's copy does not grow with the
+longest sequence the engine allows.  The layout is fixed by the capacities, so the
+same device addresses serve every step and every captured graph.  The reference
+rebuilds an int64 ``(B, max_blocks)`` table from Python lists and copies ids,
+positions and cos/sin rows separately each step (``serving/paged_decoder.py:207-257``).
+
+What a particular kind of mixer wants planned per step (the attention kernels'
+routing lists, for one) is not known here: the model's parts name ``StepPlanner``
+classes, each gets a segment of the buffer, and its result is found in
+``ctx.plans[name]``.
 """
 
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Hashable
+from typing import Any, Hashable
 
 import numpy as np
 import torch
 
 from ..cache.manager import CacheManager, pages_for
-
-QUERY_TILE = 64  # query rows per block of the mma.sync prefill kernel
-WIDE_TILE = 128  # query rows per block of the tcgen05 prefill kernel
+from ..parts.base import StepPlanner
 
 
 @dataclass
@@ -40,23 +45,6 @@ class StepEntry:
     request: Hashable
     tokens: list[int]
     want: list[int] = field(default_factory=list)  # indices into ``tokens``
-
-
-def pair_tiles(work: list[int], out) -> int:
-    """Pair query tiles for the prefill attention kernel: longest with shortest.
-
-    ``work[i]`` is the number of keys tile i attends to.  Writes pairs of tile
-    indices into ``out`` (second index -1 for an odd one out) and returns the
-    number of pairs.  A block runs the two tiles of a pair back to back, so every
-    block of a causal prompt does about the same amount of work.
-    """
-    order = sorted(range(len(work)), key=lambda i: -work[i])
-    n_pairs = (len(order) + 1) // 2
-    for k in range(n_pairs):
-        a, b = order[k], (order[len(order) - 1 - k] if len(order) - 1 - k > k else -1)
-        out[2 * k] = a
-        out[2 * k + 1] = b
-    return n_pairs
 
 
 class Workspace:
@@ -109,16 +97,6 @@ class StepContext:
     seq_slots: torch.Tensor
     block_tables: list[torch.Tensor]
     logit_rows: torch.Tensor
-    single_seqs: torch.Tensor
-    n_single: int
-    tile_seq: torch.Tensor
-    tile_start: torch.Tensor
-    n_tiles: int
-    tile_pairs: torch.Tensor
-    n_pairs: int
-    wide_seq: torch.Tensor    # the same portions cut into WIDE_TILE-query tiles, longest first
-    wide_start: torch.Tensor
-    n_wide: int
     max_kv_len: int
     max_q_len: int
     max_seqs: int
@@ -126,12 +104,17 @@ class StepContext:
     # host copies for parts that plan on the host
     q_lens: list[int] = field(default_factory=list)
     kv_lens: list[int] = field(default_factory=list)
+    plans: dict[str, Any] = field(default_factory=dict)  # what each step planner returned
     fixed_shape: bool = False  # True inside a captured decode graph (sizes are capacities)
+
+
+_FEW_ROWS = 8            # up to this many changed block-table rows are copied span by span,
+_ONE_COPY_WORDS = 1 << 16  # more of them as one block of whole rows if that stays this small
 
 
 class BatchBuilder:
     def __init__(self, cache: CacheManager, max_tokens: int, max_seqs: int, max_seq_len: int,
-                 device: torch.device):
+                 device: torch.device, planners: dict[str, type[StepPlanner]] | None = None):
         self.cache = cache
         self.device = device
         self.max_tokens = max_tokens
@@ -139,7 +122,7 @@ class BatchBuilder:
         self.max_seq_len = max_seq_len
         self.n_groups = len(cache.groups)
         self.table_len = [pages_for(max_seq_len, g.page_size) for g in cache.groups]
-        self.max_tiles = (max_tokens // QUERY_TILE + max_seqs + 2) // 2 * 2
+        self.planners: dict[str, StepPlanner] = {name: cls() for name, cls in (planners or {}).items()}
 
         off = 0
         self._off: dict[str, tuple[int, int]] = {}
@@ -151,20 +134,17 @@ class BatchBuilder:
 
         seg("cu_q", max_seqs + 1)
         seg("seq_slots", max_seqs)
-        seg("single_seqs", max_seqs)
-        seg("tile_seq", self.max_tiles)
-        seg("tile_start", self.max_tiles)
-        seg("tile_pairs", self.max_tiles + 1)
-        seg("wide_seq", self.max_tiles)
-        seg("wide_start", self.max_tiles)
-        for g in range(self.n_groups):
-            seg(f"block_table{g}", max_seqs * self.table_len[g])
         seg("token_ids", max_tokens)
         seg("positions", max_tokens)
         seg("tok_seq", max_tokens)
         seg("logit_rows", max_tokens)
         for g in range(self.n_groups):
             seg(f"kv_slots{g}", max_tokens)
+        for name, planner in self.planners.items():
+            seg(f"plan:{name}", planner.words(max_tokens, max_seqs))
+        self.front = off  # everything before this goes to the device in one copy per step
+        for g in range(self.n_groups):
+            seg(f"block_table{g}", max_seqs * self.table_len[g])
         self.total = off
         pin = device.type == "cuda"
         self.host = torch.zeros(self.total, dtype=torch.int32, pin_memory=pin)
@@ -172,6 +152,8 @@ class BatchBuilder:
         self.dev = torch.zeros(self.total, dtype=torch.int32, device=device)
         self._copied = torch.cuda.Event() if pin else None
         self._copy_pending = False
+        self.copied_words = 0  # int32 words the last build sent to the device
+        self.words_sent = 0    # and all builds so far
         # what each block-table row of the host buffer holds: (admission serial, entries written),
         # so that a request that keeps its row from step to step only appends its new pages
         self._row_owner: list[list[tuple[int, int] | None]] = [
@@ -180,6 +162,11 @@ class BatchBuilder:
         # tensor costs more than filling a decode step's numbers
         self._host_views: dict[str, np.ndarray] = {}
         self._device_views: dict[tuple, dict] = {}
+        self._plan_dev = {name: self._d(f"plan:{name}") for name in self.planners}
+        self._host_tables = [self.host[self._off[f"block_table{g}"][0]:][:max_seqs * self.table_len[g]]
+                             .view(max_seqs, self.table_len[g]) for g in range(self.n_groups)]
+        self._dev_tables = [self._d(f"block_table{g}").view(max_seqs, self.table_len[g])
+                            for g in range(self.n_groups)]
 
     def _h(self, name: str) -> np.ndarray:
         v = self._host_views.get(name)
@@ -215,17 +202,13 @@ class BatchBuilder:
         cu_q = self._h("cu_q"); seq_slots = self._h("seq_slots")
         token_ids = self._h("token_ids"); positions = self._h("positions")
         tok_seq = self._h("tok_seq"); logit_rows = self._h("logit_rows")
-        single = self._h("single_seqs"); tile_seq = self._h("tile_seq")
-        tile_start = self._h("tile_start")
-        tile_pairs = self._h("tile_pairs")
-        tile_work: list[int] = []
-        wide: list[tuple[int, int, int]] = []  # (keys its last row sees, sequence, first row)
         tables = [self._h(f"block_table{g}").reshape(self.max_seqs, self.table_len[g])
                   for g in range(self.n_groups)]
         kv_slots = [self._h(f"kv_slots{g}") for g in range(self.n_groups)]
+        dirty: list[list[tuple[int, int, int]]] = [[] for _ in range(self.n_groups)]  # (row, lo, hi)
 
-        t = 0; r = 0; n_single = 0; n_tiles = 0
-        q_lens: list[int] = []; kv_lens: list[int] = []
+        t = 0; r = 0
+        q_lens: list[int] = []; kv_lens: list[int] = []; first: list[int] = []
         cu_q[0] = 0
         for s, (e, start) in enumerate(zip(entries, starts)):
             n = len(e.tokens)
@@ -247,12 +230,14 @@ class BatchBuilder:
                 row = tables[g][s]
                 owner = self._row_owner[g][s]
                 serial = cache.admission(e.request)
-                if grp.spec.window is None and owner is not None and owner[0] == serial \
+                if grp.window is None and owner is not None and owner[0] == serial \
                         and owner[1] <= len(table):
                     if owner[1] < len(table):
                         row[owner[1]:len(table)] = table[owner[1]:]   # only the new pages
+                        dirty[g].append((s, owner[1], len(table)))
                 else:
                     row[:len(table)] = table
+                    dirty[g].append((s, 0, len(table)))
                 self._row_owner[g][s] = (serial, len(table))
                 ps = grp.page_size
                 if n == 1:
@@ -271,18 +256,7 @@ class BatchBuilder:
                     raise ValueError(f"want index {w} outside the {n} tokens of {e.request!r}")
                 logit_rows[r] = t + w
                 r += 1
-            if n == 1:
-                single[n_single] = s
-                n_single += 1
-            else:
-                for q0 in range(0, n, QUERY_TILE):
-                    tile_seq[n_tiles] = s
-                    tile_start[n_tiles] = q0
-                    tile_work.append(start + min(q0 + QUERY_TILE, n))  # keys its last row sees
-                    n_tiles += 1
-                for q0 in range(0, n, WIDE_TILE):
-                    wide.append((start + min(q0 + WIDE_TILE, n), s, q0))
-            q_lens.append(n); kv_lens.append(end)
+            q_lens.append(n); kv_lens.append(end); first.append(start)
             t += n
             cu_q[s + 1] = t
         for k in range(pad):  # padding rows: one token at position 0 on the scratch page
@@ -290,29 +264,42 @@ class BatchBuilder:
             token_ids[t] = 0; positions[t] = 0; tok_seq[t] = s
             seq_slots[s] = cache.scratch_slot
             for g, grp in enumerate(cache.groups):
-                tables[g][s, 0] = grp.scratch_page
-                self._row_owner[g][s] = None
+                if self._row_owner[g][s] != (-1, 1):
+                    tables[g][s, 0] = grp.scratch_page
+                    dirty[g].append((s, 0, 1))
+                    self._row_owner[g][s] = (-1, 1)   # no admission has serial -1
                 kv_slots[g][t] = grp.scratch_page * grp.page_size
-            single[n_single] = s; n_single += 1
             logit_rows[r] = t; r += 1
-            q_lens.append(1); kv_lens.append(1)
+            q_lens.append(1); kv_lens.append(1); first.append(0)
             t += 1
             cu_q[s + 1] = t
         S += pad; N = t
-        n_pairs = pair_tiles(tile_work, tile_pairs)
-        if wide:
-            wide.sort(key=lambda w: -w[0])
-            ws_, wq_ = self._h("wide_seq"), self._h("wide_start")
-            for i, (_, s, q0) in enumerate(wide):
-                ws_[i] = s
-                wq_[i] = q0
+        plans = {name: planner.plan(self._h(f"plan:{name}"), self._plan_dev[name], q_lens, first)
+                 for name, planner in self.planners.items()}
 
-        self.dev.copy_(self.host, non_blocking=True)
+        self.dev[:self.front].copy_(self.host[:self.front], non_blocking=True)
+        self.copied_words = self.front
+        for g in range(self.n_groups):
+            spans = dirty[g]
+            if not spans:
+                continue
+            lo_row, hi_row = min(x[0] for x in spans), max(x[0] for x in spans) + 1
+            if len(spans) > _FEW_ROWS and (hi_row - lo_row) * self.table_len[g] <= _ONE_COPY_WORDS:
+                # many rows changed (requests moved): whole rows are contiguous, one copy
+                self._dev_tables[g][lo_row:hi_row].copy_(self._host_tables[g][lo_row:hi_row],
+                                                         non_blocking=True)
+                self.copied_words += (hi_row - lo_row) * self.table_len[g]
+            else:
+                for s, lo, hi in spans:
+                    self._dev_tables[g][s, lo:hi].copy_(self._host_tables[g][s, lo:hi],
+                                                        non_blocking=True)
+                    self.copied_words += hi - lo
+        self.words_sent += self.copied_words
         if self._copied is not None:
             self._copied.record()
             self._copy_pending = True
 
-        sizes = (N, S, r, n_single, n_tiles, n_pairs, len(wide))
+        sizes = (N, S, r)
         views = self._device_views.get(sizes)
         if views is None:
             if len(self._device_views) >= 512:
@@ -322,16 +309,10 @@ class BatchBuilder:
                 tok_seq=self._d("tok_seq", N),
                 kv_slots=[self._d(f"kv_slots{g}", N) for g in range(self.n_groups)],
                 cu_q=self._d("cu_q", S + 1), seq_slots=self._d("seq_slots", S),
-                block_tables=[self._d(f"block_table{g}").view(self.max_seqs, self.table_len[g])[:S]
-                              for g in range(self.n_groups)],
-                logit_rows=self._d("logit_rows", r),
-                single_seqs=self._d("single_seqs", n_single),
-                tile_seq=self._d("tile_seq", n_tiles), tile_start=self._d("tile_start", n_tiles),
-                tile_pairs=self._d("tile_pairs", 2 * n_pairs),
-                wide_seq=self._d("wide_seq", len(wide)), wide_start=self._d("wide_start", len(wide)))
+                block_tables=[self._dev_tables[g][:S] for g in range(self.n_groups)],
+                logit_rows=self._d("logit_rows", r))
         return StepContext(
-            n_tokens=N, n_seqs=S, num_logit_rows=r, n_single=n_single, n_tiles=n_tiles,
-            n_pairs=n_pairs, n_wide=len(wide), max_kv_len=max(kv_lens) if kv_lens else 0,
+            n_tokens=N, n_seqs=S, num_logit_rows=r, max_kv_len=max(kv_lens) if kv_lens else 0,
             max_q_len=max(q_lens) if q_lens else 0, max_seqs=self.max_seqs, ws=ws, q_lens=q_lens,
-            kv_lens=kv_lens, **views,
+            kv_lens=kv_lens, plans=plans, **views,
         )

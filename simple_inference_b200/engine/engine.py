@@ -89,9 +89,12 @@ class InferenceEngine:
         self.max_tokens_per_step = max_tokens_per_step or max(max_running, 2048)
         self.num_kv_blocks = (num_kv_blocks if num_kv_blocks is not None
                               else max_running * pages_for(max_seq_len, block_size))
+        # by default every group gets enough pages of its own size for max_running full requests
+        pool_pages = (num_kv_blocks if num_kv_blocks is not None
+                      else lambda page: max_running * pages_for(max_seq_len, page))
 
         self.scheduler = Scheduler(max_running, self.max_tokens_per_step, chunk_size, token_budget)
-        self.cache = CacheManager(model.cache_specs(), block_size, self.num_kv_blocks, max_running,
+        self.cache = CacheManager(model.cache_specs(), block_size, pool_pages, max_running,
                                   self.max_tokens_per_step, dtype=self.rt.dtype,
                                   device=self.rt.device)
         self.runner = ModelRunner(model, self.cache, self.rt, self.max_tokens_per_step,

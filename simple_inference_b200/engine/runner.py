@@ -49,7 +49,8 @@ class ModelRunner:
         self.max_seq_len = max_seq_len
         self.ws = Workspace(rt.device, max_step_tokens,
                             max_logit_rows if max_logit_rows is not None else max_seqs)
-        self.builder = BatchBuilder(cache, max_step_tokens, max_seqs, max_seq_len, rt.device)
+        self.builder = BatchBuilder(cache, max_step_tokens, max_seqs, max_seq_len, rt.device,
+                                    planners=model.step_planners())
         self.layer_caches = cache.layer_caches()
         self.cuda_graphs = cuda_graphs and rt.device.type == "cuda"
         self._graphs: dict[int, tuple[torch.cuda.CUDAGraph, torch.Tensor]] = {}
@@ -104,10 +105,10 @@ class ModelRunner:
 
     def _replay(self, entries: list[StepEntry], starts: list[int]) -> torch.Tensor:
         bucket = self.bucket_for(len(entries))
+        if bucket not in self._graphs:   # first met inside a live step: capture on padding rows
+            self._capture(bucket)
         ctx = self._fixed_context(entries, starts, bucket)
         self.last_context = ctx
-        if bucket not in self._graphs:
-            self._capture(bucket, ctx)
         graph, logits = self._graphs[bucket]
         graph.replay()
         self.replayed_kernels += self._graph_kernels[bucket]
@@ -116,12 +117,15 @@ class ModelRunner:
             rows = self._logit_rows[(bucket, len(entries))] = logits[:len(entries)]
         return rows
 
-    def _capture(self, bucket: int, ctx: StepContext) -> None:
+    def _capture(self, bucket: int) -> None:
         """Warm up on a side stream, then record one forward (reference model/cuda_graph.py:62-88).
 
-        The warm-up runs really execute the step, and so does nothing the
-        replay would not do again: the same tokens write the same cache slots.
+        Always on padding rows alone: they read and write only the scratch page and the
+        scratch slot, so neither the warm-up runs nor the recording touch what a live request
+        holds.  (Running a live step several times would be harmless for keys and values,
+        which land in the same slots each time, but not for a mixer that advances a state.)
         """
+        ctx = self._fixed_context([], [], bucket)
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
@@ -140,10 +144,9 @@ class ModelRunner:
         self._graphs[bucket] = (graph, logits)
 
     def capture_all(self) -> None:
-        """Capture the decode graph of every bucket ahead of time, on padding rows only."""
+        """Capture the decode graph of every bucket ahead of time."""
         if not self.cuda_graphs:
             return
         for bucket in self._buckets:
             if bucket not in self._graphs:
-                ctx = self._fixed_context([], [], bucket)
-                self._capture(bucket, ctx)
+                self._capture(bucket)

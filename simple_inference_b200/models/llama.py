@@ -52,9 +52,9 @@ def llama_plan(cfg: LlamaConfig) -> ModelPlan:
         run_order=ModelPlan.sequential(cfg.num_hidden_layers),
         final_norm=PartSpec("rmsnorm", {"hidden_size": cfg.hidden_size, "eps": cfg.rms_norm_eps}),
         tie_embeddings=cfg.tie_word_embeddings,
-        embedding_name="model.embed_tokens.weight",
+        embedding_names={"weight": "model.embed_tokens.weight"},
         final_norm_names={"weight": "model.norm.weight"},
-        head_name="lm_head.weight",
+        head_names={"weight": "lm_head.weight"},
         max_positions=cfg.max_position_embeddings,
         eos_token_ids=cfg.eos_ids(),
         bos_token_id=cfg.bos_token_id,

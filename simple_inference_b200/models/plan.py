@@ -1,9 +1,9 @@
 """A model as data: parts chosen layer by layer, and the order layers run in.
 
 An architecture module turns its typed configuration into a ``ModelPlan``:
-the embedding, a list of ``LayerPlan`` (each a block ``PartSpec`` plus the
-checkpoint name of every tensor it needs), the run order, the final norm and
-the output head.  ``DecoderModel`` builds the parts through the registries,
+the embedding (a registered kind), a list of ``LayerPlan`` (each a block
+``PartSpec`` plus the checkpoint name of every tensor it needs), the run order, the
+final norm and the output head (a registered kind too).  ``DecoderModel`` builds the parts through the registries,
 binds the loaded tensors and executes the plan for a step; it knows nothing of
 any particular architecture.
 
@@ -22,9 +22,8 @@ from dataclasses import dataclass, field
 
 import torch
 
-from ..parts.base import Block, CacheSpec, LayerCache, PartSpec, Runtime, TensorSpec
-from ..parts.embedding import OutputHead, TokenEmbedding
-from ..parts.registry import BLOCKS, NORMS
+from ..parts.base import Block, CacheSpec, LayerCache, PartSpec, Runtime, StepPlanner, TensorSpec
+from ..parts.registry import BLOCKS, EMBEDDINGS, HEADS, NORMS
 
 
 @dataclass
@@ -49,12 +48,23 @@ class ModelPlan:
     run_order: list[RunStep]
     final_norm: PartSpec
     tie_embeddings: bool
-    embedding_name: str
+    embedding_names: dict[str, str]      # embedding-local tensor name -> name in the checkpoint
     final_norm_names: dict[str, str]
-    head_name: str | None
+    head_names: dict[str, str]           # tensors of the head (not needed when it is tied)
     max_positions: int
     eos_token_ids: tuple[int, ...] = ()
     bos_token_id: int | None = None
+    embedding: PartSpec | None = None    # default: the plain lookup ``token_embedding``
+    head: PartSpec | None = None         # default: ``linear_head``, tied as ``tie_embeddings`` says
+
+    def embedding_spec(self) -> PartSpec:
+        return self.embedding or PartSpec("token_embedding", {
+            "vocab_size": self.vocab_size, "hidden_size": self.hidden_size})
+
+    def head_spec(self) -> PartSpec:
+        return self.head or PartSpec("linear_head", {
+            "vocab_size": self.vocab_size, "hidden_size": self.hidden_size,
+            "tied": self.tie_embeddings})
 
     @staticmethod
     def sequential(num_layers: int) -> list[RunStep]:
@@ -73,10 +83,10 @@ class DecoderModel:
 
     def __init__(self, plan: ModelPlan):
         self.plan = plan
-        self.embedding = TokenEmbedding(plan.vocab_size, plan.hidden_size)
+        self.embedding = EMBEDDINGS.build(plan.embedding_spec())
         self.blocks: list[Block] = [BLOCKS.build(lp.block) for lp in plan.layers]
         self.final_norm = NORMS.build(plan.final_norm)
-        self.head = OutputHead(plan.vocab_size, plan.hidden_size, plan.tie_embeddings)
+        self.head = HEADS.build(plan.head_spec())
         self.rt: Runtime | None = None
         self._check_run_order()
 
@@ -111,35 +121,44 @@ class DecoderModel:
 
     def tensor_specs(self) -> dict[str, TensorSpec]:
         """Checkpoint tensor name -> spec, for the loader and the random-weights writer."""
-        out: dict[str, TensorSpec] = {
-            self.plan.embedding_name: self.embedding.tensors()["weight"],
-        }
+        out: dict[str, TensorSpec] = {}
+        for local, spec in self.embedding.tensors().items():
+            out[self.plan.embedding_names[local]] = spec
         for lp, block in zip(self.plan.layers, self.blocks):
             for local, spec in block.tensors().items():
                 out[lp.tensor_names[local]] = spec
         for local, spec in self.final_norm.tensors().items():
             out[self.plan.final_norm_names[local]] = spec
-        if not self.plan.tie_embeddings:
-            out[self.plan.head_name] = self.head.tensors()["weight"]
+        for local, spec in self.head.tensors().items():
+            out[self.plan.head_names[local]] = spec
+        return out
+
+    def step_planners(self) -> dict[str, type[StepPlanner]]:
+        """The step planner classes the model's parts ask for, one per name."""
+        out: dict[str, type[StepPlanner]] = {}
+        for part in (self.embedding, *self.blocks, self.final_norm, self.head):
+            for planner in part.step_planners():
+                out.setdefault(planner.name, planner)
         return out
 
     def optional_tensor_names(self) -> set[str]:
         """Names a checkpoint may carry that the model does not need."""
-        if self.plan.tie_embeddings and self.plan.head_name:
-            return {self.plan.head_name}  # a tied checkpoint may still store the head
+        if self.plan.tie_embeddings:  # a tied checkpoint may still store the head
+            return set(self.plan.head_names.values()) - set(self.tensor_specs())
         return set()
 
     # -------------------------------------------------------------- weights
     def bind(self, tensors: dict[str, torch.Tensor], rt: Runtime) -> None:
         """``tensors``: checkpoint name -> device tensor in its final dtype."""
         self.rt = rt
-        self.embedding.bind({"weight": tensors[self.plan.embedding_name]}, rt)
+        self.embedding.bind({local: tensors[name]
+                             for local, name in self.plan.embedding_names.items()}, rt)
         for lp, block in zip(self.plan.layers, self.blocks):
             block.bind({local: tensors[name] for local, name in lp.tensor_names.items()}, rt)
         self.final_norm.bind({local: tensors[name]
                               for local, name in self.plan.final_norm_names.items()}, rt)
-        head_t = {} if self.plan.tie_embeddings else {"weight": tensors[self.plan.head_name]}
-        self.head.bind(head_t, rt, embedding=self.embedding)
+        self.head.bind({local: tensors[self.plan.head_names[local]]
+                        for local in self.head.tensors()}, rt, embedding=self.embedding)
 
     # ----------------------------------------------------------------- step
     def forward(self, ctx, caches: list[LayerCache | None]) -> torch.Tensor:

@@ -370,21 +370,23 @@ def attention_generic(q: torch.Tensor, pool: torch.Tensor, block_table: torch.Te
 
 
 MAX_KV_SPLITS = 32
-# Cost model of the decode-attention kernel, fitted to timings on the 3B shape (24 query heads
-# in 8 groups, head size 128, 1 to 64 sequences, 512 to 8192 keys): a block costs a fixed
-# part plus a part per 64-key tile, the blocks run in waves of as many as fit on the GPU
-# (3 per SM), and joining the splits costs a little more with each split.
+# Cost model of the decode-attention kernel: a block costs a fixed part plus a part per
+# 64-key tile, the blocks run in waves of as many as fit on the GPU (3 per SM), and joining the
+# splits costs a little more with each split.  The constants are timings of heads of 128 (1 to
+# 64 sequences, 512 to 8192 keys, 1 to 8 kv heads); a tile's part is its bytes and scales
+# with the head size.
 _RESIDENT_BLOCKS = 3 * 148
-_BLOCK_US, _TILE_US, _MERGE_US, _MERGE_SPLIT_US = 6.0, 0.8, 2.0, 0.3
+_BLOCK_US, _TILE_US_AT_128, _MERGE_US, _MERGE_SPLIT_US = 6.0, 0.8, 2.0, 0.3
 
 
 @functools.lru_cache(maxsize=4096)
-def _plan_kv_splits(base: int, tiles: int) -> int:
+def _plan_kv_splits(base: int, tiles: int, head_dim: int) -> int:
+    tile_us = _TILE_US_AT_128 * head_dim / 128.0
     best, best_t = 1, float("inf")
     for s in range(1, min(MAX_KV_SPLITS, tiles) + 1):
         per = -(-tiles // s)
         waves = -(-base * s // _RESIDENT_BLOCKS)
-        t = waves * (_BLOCK_US + per * _TILE_US)
+        t = waves * (_BLOCK_US + per * tile_us)
         if s > 1:
             t += _MERGE_US + s * _MERGE_SPLIT_US
         if t < best_t - 1e-9:
@@ -392,24 +394,26 @@ def _plan_kv_splits(base: int, tiles: int) -> int:
     return best
 
 
-def plan_kv_splits(n_single: int, num_q_heads: int, num_kv_heads: int, max_kv_len: int) -> int:
+def plan_kv_splits(n_single: int, num_q_heads: int, num_kv_heads: int, max_kv_len: int,
+                   head_dim: int = 128) -> int:
     """How many blocks share the keys of one (sequence, kv head) in the decode kernel:
     the number that the cost model above makes cheapest."""
     group = num_q_heads // num_kv_heads
     base = max(1, n_single * num_kv_heads * ((group + 15) // 16))
     tiles = max(1, (max_kv_len + 63) // 64)
-    return _plan_kv_splits(base, tiles)
+    return _plan_kv_splits(base, tiles, head_dim)
 
 
-def paged_attention(q: torch.Tensor, pool: torch.Tensor, ctx, group: int, out: torch.Tensor,
+def paged_attention(q: torch.Tensor, pool: torch.Tensor, ctx, plan, group: int, out: torch.Tensor,
                     num_q_heads: int, num_kv_heads: int, head_dim: int, scale: float,
                     window: int | None) -> torch.Tensor:
     """Attention of a step's tokens over the pages of layer group ``group``.
 
-    ``ctx`` is the step's ``StepContext``.  float32: the generic kernel for every
-    token.  bfloat16: tensor-core kernels, one for sequences that bring a single
-    token (keys split over blocks, partial results joined through scratch memory)
-    and one for longer portions (64-query tiles).
+    ``ctx`` is the step's ``StepContext``, ``plan`` its ``AttentionStepPlan``
+    (``parts/attention_plan.py``; not needed in float32).  float32: the generic kernel
+    for every token.  bfloat16: tensor-core kernels, one for sequences that bring a
+    single token (keys split over blocks, partial results joined through scratch
+    memory) and one for longer portions (64-query or 128-query tiles).
     """
     table = ctx.block_tables[group]
     if q.dtype == torch.float32:
@@ -424,26 +428,26 @@ def paged_attention(q: torch.Tensor, pool: torch.Tensor, ctx, group: int, out: t
         raise KernelError("attention: pool/out shape or dtype does not fit")
     lib = attention_library(head_dim)
     win = int(window or 0)
-    if ctx.n_tiles and wide_prefill_fits(ctx, head_dim, page_size):
-        attention_prefill_wide(q, pool, ctx, group, out, num_q_heads, num_kv_heads, head_dim, scale,
-                               window)
-    elif ctx.n_tiles:
+    if plan.n_tiles and wide_prefill_fits(plan, head_dim, page_size):
+        attention_prefill_wide(q, pool, ctx, plan, group, out, num_q_heads, num_kv_heads, head_dim,
+                               scale, window)
+    elif plan.n_tiles:
         _check(lib.si_attn_prefill(
             _p(q), q.stride(0), _p(pool), _p(table), table.stride(0), _p(ctx.cu_q),
-            _p(ctx.positions), _p(ctx.tile_seq), _p(ctx.tile_start), _p(ctx.tile_pairs),
-            ctx.n_pairs, _p(out),
+            _p(ctx.positions), _p(plan.tile_seq), _p(plan.tile_start), _p(plan.tile_pairs),
+            plan.n_pairs, _p(out),
             out.stride(0), num_q_heads, num_kv_heads, page_size, _c_float(scale), win, _stream()),
             "attn_prefill")
-    if ctx.n_single:
-        n_splits = plan_kv_splits(ctx.n_single, num_q_heads, num_kv_heads, ctx.max_kv_len)
+    if plan.n_single:
+        n_splits = plan_kv_splits(plan.n_single, num_q_heads, num_kv_heads, ctx.max_kv_len, head_dim)
         scratch = None
         if n_splits > 1:
             scratch = ctx.ws.get("attn.split",
-                                 (ctx.n_single, num_q_heads * MAX_KV_SPLITS * (head_dim + 2)),
+                                 (plan.n_single, num_q_heads * MAX_KV_SPLITS * (head_dim + 2)),
                                  torch.float32, row_cap=ctx.max_seqs)
         _check(lib.si_attn_decode(
             _p(q), q.stride(0), _p(pool), pool.shape[0], _p(table), table.stride(0), _p(ctx.cu_q),
-            _p(ctx.positions), _p(ctx.single_seqs), ctx.n_single, _p(out), out.stride(0),
+            _p(ctx.positions), _p(plan.single_seqs), plan.n_single, _p(out), out.stride(0),
             _p(scratch), num_q_heads, num_kv_heads, page_size, _c_float(scale), win, n_splits,
             _stream()), "attn_decode", kernels=2 if n_splits > 1 else 1)
     return out
@@ -452,17 +456,17 @@ def paged_attention(q: torch.Tensor, pool: torch.Tensor, ctx, group: int, out: t
 WIDE_MIN_QUERIES = 64  # shorter portions stay on the 64-query mma.sync tiles
 
 
-def wide_prefill_fits(ctx, head_dim: int, page_size: int) -> bool:
+def wide_prefill_fits(plan, head_dim: int, page_size: int) -> bool:
     """Whether the tcgen05 prefill kernel takes this step's portions: it is written for heads
     of 128 and pages of 8, 16, 32 or 64 tokens, and pays off from 64 queries a portion."""
     return head_dim == 128 and page_size in (8, 16, 32, 64) and \
-        getattr(ctx, "n_wide", 0) > 0 and getattr(ctx, "max_q_len", 0) >= WIDE_MIN_QUERIES
+        plan.n_wide > 0 and plan.max_q_len >= WIDE_MIN_QUERIES
 
 
-def attention_prefill_wide(q: torch.Tensor, pool: torch.Tensor, ctx, group: int, out: torch.Tensor,
-                           num_q_heads: int, num_kv_heads: int, head_dim: int, scale: float,
-                           window: int | None) -> torch.Tensor:
-    """The tcgen05 prefill kernel on the step's 128-query tiles (``ctx.wide_seq/wide_start``).
+def attention_prefill_wide(q: torch.Tensor, pool: torch.Tensor, ctx, plan, group: int,
+                           out: torch.Tensor, num_q_heads: int, num_kv_heads: int, head_dim: int,
+                           scale: float, window: int | None) -> torch.Tensor:
+    """The tcgen05 prefill kernel on the step's 128-query tiles (``plan.wide_seq/wide_start``).
 
     ``q`` is the query part of the fused projection output, a view with its row stride.
     """
@@ -477,7 +481,7 @@ def attention_prefill_wide(q: torch.Tensor, pool: torch.Tensor, ctx, group: int,
         raise KernelError(f"attention_prefill_wide: no tcgen05 kernel for head size {head_dim}")
     _check(lib.si_attn_prefill_tc(
         _p(q), q.stride(0), q.shape[0], _p(pool), pool.shape[0], _p(table), table.stride(0),
-        _p(ctx.cu_q), _p(ctx.positions), _p(ctx.wide_seq), _p(ctx.wide_start), ctx.n_wide, _p(out),
+        _p(ctx.cu_q), _p(ctx.positions), _p(plan.wide_seq), _p(plan.wide_start), plan.n_wide, _p(out),
         out.stride(0), num_q_heads, num_kv_heads, page_size, _c_float(scale), int(window or 0),
         _stream()), "attn_prefill_tc")
     return out

@@ -22,7 +22,8 @@ import math
 import torch
 
 from .. import ops
-from .base import LayerCache, Mixer, PagedKVSpec, PartSpec, Runtime, TensorSpec
+from .attention_plan import PagedAttentionPlanner
+from .base import LayerCache, Mixer, PagedKVSpec, PartSpec, Runtime, StepPlanner, TensorSpec
 from .registry import POSITION_ENCODINGS, register_mixer
 
 
@@ -58,6 +59,9 @@ class PagedAttention(Mixer):
     def cache_spec(self) -> PagedKVSpec:
         return PagedKVSpec(self.num_kv_heads, self.head_dim, self.window)
 
+    def step_planners(self) -> list[type[StepPlanner]]:
+        return [PagedAttentionPlanner]  # which kernel each sequence of the step goes to
+
     def bind(self, tensors: dict[str, torch.Tensor], rt: Runtime) -> None:
         super().bind(tensors, rt)
         self.w_qkv = torch.cat([tensors["wq"], tensors["wk"], tensors["wv"]], dim=0).contiguous()
@@ -70,7 +74,8 @@ class PagedAttention(Mixer):
         self.position.project_encode_and_store(x, self.w_qkv, qkv, self.num_heads,
                                                self.num_kv_heads, self.head_dim, ctx, cache)
         mixed = ctx.ws.get("attn.mixed", (n, self.q_width), x.dtype)
-        ops.paged_attention(qkv, cache.pool, ctx, cache.group, mixed, self.num_heads,
+        ops.paged_attention(qkv, cache.pool, ctx, ctx.plans.get(PagedAttentionPlanner.name),
+                            cache.group, mixed, self.num_heads,
                             self.num_kv_heads, self.head_dim, self.scale, self.window)
         out = ctx.ws.get("attn.proj", (n, self.hidden_size), x.dtype)
         ops.linear(mixed, self.w_o, out)

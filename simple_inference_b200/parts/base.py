@@ -56,11 +56,20 @@ class PagedKVSpec:
 
     ``window`` None keeps every key; an integer w lets a query at position p see
     keys in (p - w, p] only, so pages wholly before that range are given back.
+    ``page_size`` None takes the cache manager's page size; a number gives this
+    kind of cache pages of its own size.
     """
 
     num_kv_heads: int
     head_dim: int
     window: int | None = None
+    page_size: int | None = None
+
+    storage = "pages"
+
+    def page_shape(self, page_size: int) -> tuple[int, ...]:
+        """One page of one cache entry: keys then values, ``[2, kv_heads, page_size, head_dim]``."""
+        return (2, self.num_kv_heads, page_size, self.head_dim)
 
 
 @dataclass(frozen=True)
@@ -70,7 +79,18 @@ class StateSpec:
     shape: tuple[int, ...]
     dtype: str = "float32"
 
+    storage = "slots"
 
+    def slot_shape(self) -> tuple[int, ...]:
+        return tuple(self.shape)
+
+
+# What a mixer may return from ``cache_spec()``.  The cache manager knows two ways of
+# storing: ``storage == "pages"`` (memory that grows with the request: the spec says how one
+# page of ``page_size`` tokens is shaped, ``page_shape(page_size)``, which page size it wants,
+# ``page_size`` or None, and whether old pages may go, ``window``) and ``storage == "slots"``
+# (one row of ``slot_shape()`` per request).  Specs that compare equal share a group of pages.
+# Any frozen dataclass with these attributes will do; the two above are the built-in ones.
 CacheSpec = PagedKVSpec | StateSpec
 
 
@@ -78,11 +98,12 @@ CacheSpec = PagedKVSpec | StateSpec
 class LayerCache:
     """What one run of a layer sees of the cache.
 
-    For a ``PagedKVSpec``: ``pool`` is ``[pages+1, 2, kv_heads, page_size,
-    head_dim]`` (index 0/1 of the second axis = keys/values; the last page is
-    scratch), ``group`` selects this layer group's block tables and write slots
-    in the ``StepContext``.  For a ``StateSpec``: ``state`` is
-    ``[slots+1, *shape]``, row = the request's slot, the last row is scratch.
+    For a spec stored in pages: ``pool`` is ``[pages+1, *spec.page_shape(page_size)]``
+    (for ``PagedKVSpec`` ``[pages+1, 2, kv_heads, page_size, head_dim]``, index 0/1 of
+    the second axis = keys/values; the last page is scratch), ``group`` selects this
+    layer group's block tables and write slots in the ``StepContext``.  For a spec
+    stored in slots: ``state`` is ``[slots+1, *spec.slot_shape()]``, row = the
+    request's slot, the last row is scratch.
     ``writes`` is False when the layer only reads a cache that another layer
     filled.
     """
@@ -120,6 +141,33 @@ class Part:
     def bind(self, tensors: dict[str, torch.Tensor], rt: Runtime) -> None:
         """Take ownership of the loaded tensors (already on device, right dtype)."""
         self.rt = rt
+
+    def step_planners(self) -> list[type["StepPlanner"]]:
+        """Classes of the host-side planners this part (or the parts inside it) wants run once
+        per step; every batch builder makes its own instance of each."""
+        return []
+
+
+class StepPlanner:
+    """Host work a kind of part needs once per step, whatever the number of layers of that kind.
+
+    The batch builder makes one instance per ``name`` and gives it a segment of the step's
+    description buffer: ``words(max_tokens, max_seqs)`` int32 words in pinned host memory
+    and the same words on the device, copied with the rest of the description in the step's
+    one host-to-device copy.  ``plan`` fills the host segment from the step's shape and
+    returns whatever its parts want to find in ``ctx.plans[name]`` (views of the device
+    segment, counts, launch shapes).
+    """
+
+    name: str = ""
+
+    def words(self, max_tokens: int, max_seqs: int) -> int:
+        return 0
+
+    def plan(self, host, dev: torch.Tensor, q_lens: list[int], starts: list[int]):
+        """``q_lens[s]`` tokens of sequence s start at position ``starts[s]``; padding rows of a
+        fixed-size batch are included (one token at position 0)."""
+        raise NotImplementedError
 
 
 class Norm(Part):
@@ -167,6 +215,31 @@ class PositionEncoding(Part):
         self.encode_and_store(qkv, num_q_heads, num_kv_heads, head_dim, ctx, cache)
 
 
+class Embedding(Part):
+    """Token ids -> rows of the float32 residual stream ``[tokens, hidden]``."""
+
+    def forward(self, token_ids: torch.Tensor, ctx: "StepContext") -> torch.Tensor:
+        raise NotImplementedError
+
+    def output_matrix(self) -> torch.Tensor:
+        """The ``[vocab, hidden]`` matrix a tied output head multiplies by."""
+        raise NotImplementedError
+
+
+class Head(Part):
+    """Normalised rows ``[rows, hidden]`` -> float32 logits ``[rows, vocab]``.
+
+    ``bind`` also receives the model's embedding: a tied head takes its matrix from there.
+    """
+
+    def bind(self, tensors: dict[str, torch.Tensor], rt: Runtime,
+             embedding: "Embedding | None" = None) -> None:
+        super().bind(tensors, rt)
+
+    def forward(self, x: torch.Tensor, ctx: "StepContext") -> torch.Tensor:
+        raise NotImplementedError
+
+
 class Mixer(Part):
     """Mixes information across the tokens of a request (attention, or a state)."""
 
@@ -197,6 +270,9 @@ class Block(Part):
     def forward(self, residual: torch.Tensor, delta: torch.Tensor | None,
                 ctx: "StepContext", cache: LayerCache | None) -> torch.Tensor:
         raise NotImplementedError
+
+    def step_planners(self) -> list[type[StepPlanner]]:
+        return self.mixer.step_planners()
 
 
 @dataclass(frozen=True)

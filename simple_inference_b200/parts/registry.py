@@ -9,7 +9,7 @@ from __future__ import annotations
 
 from typing import Any, Callable
 
-from .base import Block, FeedForward, Mixer, Norm, Part, PartSpec, PositionEncoding
+from .base import Block, Embedding, FeedForward, Head, Mixer, Norm, Part, PartSpec, PositionEncoding
 
 
 class UnknownPartError(KeyError):
@@ -50,9 +50,13 @@ FEED_FORWARDS = _Registry("feed-forward", FeedForward)
 NORMS = _Registry("norm", Norm)
 POSITION_ENCODINGS = _Registry("position encoding", PositionEncoding)
 BLOCKS = _Registry("block", Block)
+EMBEDDINGS = _Registry("embedding", Embedding)
+HEADS = _Registry("output head", Head)
 
 register_mixer = MIXERS.register
 register_feed_forward = FEED_FORWARDS.register
 register_norm = NORMS.register
 register_position_encoding = POSITION_ENCODINGS.register
 register_block = BLOCKS.register
+register_embedding = EMBEDDINGS.register
+register_head = HEADS.register

@@ -29,6 +29,11 @@ class Sampler:
         self._out_host = torch.zeros(max_rows, dtype=torch.int32, pin_memory=pin)
         self._status_host = torch.zeros(1, dtype=torch.int32, pin_memory=pin)
 
+    @property
+    def host_bytes(self) -> int:
+        """Bytes of options copied to the device per call of ``sample``."""
+        return self._host.numel() * 4
+
     def _field(self, buf, i: int, n: int):
         return buf[i * self.max_rows: i * self.max_rows + n]
 

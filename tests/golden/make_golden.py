@@ -14,6 +14,10 @@ runs one prompt through both and stores
     golden_<name>.json   prompt ids, the reference's logits at the last 4
                          positions (first 16 vocabulary entries) and the
                          reference's argmax at every position
+    golden_sampling.json rows of logits (with ties) and, for several settings of
+                         temperature, top-k and top-p, which entries the reference's
+                         filters keep (``sampling.py:39-52,69-128``, composed in the
+                         order of its ``sample``, ``:159-167``)
 
 ``tests/test_plain.py`` recomputes these with the plain implementation alone, so
 the oracle of all other tests stays anchored to the reference without the
@@ -82,11 +86,51 @@ def reference_logits(ref_root: str, cfg: dict, w: dict, ids: list[int]) -> torch
     return x @ head.T
 
 
+SAMPLING_SETTINGS = [(1.0, 0, 1.0), (0.7, 5, 1.0), (1.3, 0, 0.9), (0.8, 20, 0.5), (1.0, 3, 0.0),
+                     (2.0, 64, 0.3), (0.5, 1, 0.99), (1.0, 0, 0.05), (1.0, 7, 1.0), (0.9, 100, 0.95)]
+
+
+def sampling_rows() -> torch.Tensor:
+    """Rows of 64 logits: random, with exact ties at the top and at the top-k edge, one peaked."""
+    g = torch.Generator().manual_seed(5)
+    rows = torch.randn(4, 64, generator=g) * 2.0
+    rows[1, 10] = rows[1, 20] = rows[1].max() + 0.5          # a tie for the top
+    order = rows[2].argsort(descending=True)
+    rows[2, order[6]] = rows[2, order[7]] = rows[2, order[5]] - 0.25   # a tie across the 7th place
+    rows[3, 33] = rows[3].max() + 9.0                        # one token holds nearly all the mass
+    return rows
+
+
+def reference_kept(ref_root: str, rows: torch.Tensor) -> list[list[list[int]]]:
+    if ref_root not in sys.path:
+        sys.path.insert(0, ref_root)
+    import sampling as ref  # type: ignore
+    out = []
+    for temperature, top_k, top_p in SAMPLING_SETTINGS:
+        z = ref.apply_temperature(rows.clone(), temperature)
+        if top_k > 0:
+            z = ref.filter_top_k(z, top_k)
+        if top_p < 1.0:
+            z = ref.filter_top_p(z, top_p)
+        out.append([torch.isfinite(r).nonzero().flatten().tolist() for r in z])
+    return out
+
+
 def main() -> None:
     if len(sys.argv) != 2:
         raise SystemExit("usage: python tests/golden/make_golden.py <folder of the reference project>")
     ref_root = sys.argv[1]
     here = Path(__file__).resolve().parent
+    rows = sampling_rows()
+    kept = reference_kept(ref_root, rows)
+    for (temperature, top_k, top_p), per_row in zip(SAMPLING_SETTINGS, kept):
+        for row, want in zip(rows, per_row):
+            mine = torch.isfinite(plain_llama.filter_logits(row, temperature, top_k, top_p))
+            assert mine.nonzero().flatten().tolist() == want, (temperature, top_k, top_p)
+    print(f"sampling filters: plain keeps what the reference keeps in all "
+          f"{len(SAMPLING_SETTINGS) * len(rows)} cases")
+    with open(here / "golden_sampling.json", "w") as f:
+        json.dump({"rows": rows.tolist(), "settings": SAMPLING_SETTINGS, "reference_kept": kept}, f)
     for name, cfg in (("A", TINY_A), ("B", TINY_B)):
         cfg = dict(cfg, torch_dtype="float32")
         with tempfile.TemporaryDirectory() as tmp:

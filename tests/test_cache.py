@@ -168,3 +168,43 @@ def test_random_orders_keep_every_invariant(seed):
         m.release(r)
     m.check()
     assert all(g.allocator.free_pages == g.num_pages for g in m.groups) and m.free_slots == 4
+
+
+def test_a_spec_of_another_kind_shapes_its_own_pages_and_names_its_own_page_size():
+    """The manager only counts pages: a cache kind it has never seen (one vector per token, in
+    pages of its own size) says how a page is shaped; groups of different page sizes live side
+    by side, each with tables and allocators of its own."""
+    from dataclasses import dataclass
+
+    @dataclass(frozen=True)
+    class VectorPerToken:
+        width: int
+        window: int | None = None
+        page_size: int | None = 8
+        storage = "pages"
+
+        def page_shape(self, page_size):
+            return (page_size, self.width)
+
+    specs = [PagedKVSpec(2, 16), VectorPerToken(5), PagedKVSpec(2, 16), VectorPerToken(5), None,
+             StateSpec((3,))]
+    m = CacheManager(specs, 4, lambda page: 64 // page, 2, 16, torch.float32, "cpu")
+    assert [g.entries for g in m.groups] == [[0, 2], [1, 3]]
+    assert [g.page_size for g in m.groups] == [4, 8] and [g.num_pages for g in m.groups] == [16, 8]
+    assert m.groups[0].pool.shape == (2, 17, 2, 2, 4, 16) and m.groups[1].pool.shape == (2, 9, 8, 5)
+    views = m.layer_caches()
+    assert views[1].pool.shape == (9, 8, 5) and views[1].page_size == 8 and views[1].group == 1
+    assert views[4] is None and views[5].state.shape == (3, 3)
+    m.admit("a", 30)
+    m.extend("a", 13)
+    assert len(m.block_table("a", 0)) == 4 and len(m.block_table("a", 1)) == 2
+    assert m.write_slot("a", 1, 12) == m.block_table("a", 1)[1] * 8 + 4
+    assert not m.can_admit(40) and m.can_admit(32)      # 8 pages of 4 and 4 pages of 8 are promised
+    m.check()
+    m.release("a")
+    assert m.free_pages(0) == 16 and m.free_pages(1) == 8
+    with pytest.raises(ValueError):
+        @dataclass(frozen=True)
+        class Odd:
+            storage = "elsewhere"
+        CacheManager([Odd()], 4, 8, 1, 4, torch.float32, "cpu")

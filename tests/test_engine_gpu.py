@@ -56,10 +56,14 @@ def test_greedy_bfloat16_graphs_on_and_off_agree_with_plain(name, model_folders)
         reqs = [eng.add_request(p, 12) for p in prompts]
         eng.run()
         outs.append([r.generated for r in reqs])
-    # The same kernels run inside and outside the graph.  Padding rows of a bucket must
-    # not disturb real rows: compare token by token, allowing a split only where the plain
-    # model's top two logits are within bfloat16 noise of each other.
-    for a, b, p in zip(outs[0], outs[1], prompts):
+    _agree_where_the_plain_model_is_sure(cfg, w, prompts, outs[0], outs[1])
+
+
+def _agree_where_the_plain_model_is_sure(cfg, w, prompts, with_graphs, without):
+    """The same kernels run inside and outside the graph.  Padding rows of a bucket must
+    not disturb real rows: compare token by token, allowing a split only where the plain
+    model's top two logits are within bfloat16 noise of each other."""
+    for a, b, p in zip(with_graphs, without, prompts):
         ids = list(p)
         for x, y in zip(a, b):
             logits = plain_llama.forward(cfg, w, ids)[-1]
@@ -68,6 +72,29 @@ def test_greedy_bfloat16_graphs_on_and_off_agree_with_plain(name, model_folders)
                 assert (top2[0] - top2[1]) < 0.05, "engines disagree where the plain model is sure"
                 break
             ids.append(x)
+
+
+@pytest.mark.parametrize("name", ["B", "D"])
+def test_forty_requests_decoding_together(name, model_folders):
+    """max_running 64 and forty short prompts: decoding runs in the graph buckets of 32 and 64
+    (with up to 24 padding rows), through the matrix products for 17 to 64 rows and the split
+    planning for many sequences; greedy tokens against the plain model."""
+    cfg, w = plain_llama.read_folder(model_folders[name])
+    top = min(60, cfg["max_position_embeddings"] - 16)
+    prompts = [random_ids(3 + (7 * i) % top, cfg["vocab_size"], 300 + i) for i in range(40)]
+    outs = []
+    for graphs in (True, False):
+        eng = _engine(model_folders[name], "bfloat16", use_cuda_graphs=graphs, max_running=64,
+                      block_size=16, max_tokens_per_step=256, chunk_size=None)
+        reqs = [eng.add_request(p, 8 + i % 5) for i, p in enumerate(prompts)]
+        live = []
+        while eng.has_work():
+            eng.step()
+            live.append(sum(r.state.value == "decode" for r in eng.scheduler.running))
+        assert max(live) > 32, "the run must reach the largest bucket"
+        outs.append([r.generated for r in reqs])
+        eng.cache.check()
+    _agree_where_the_plain_model_is_sure(cfg, w, prompts, outs[0], outs[1])
 
 
 def test_temperature_sampling_matches_the_plain_sampler(model_folders):

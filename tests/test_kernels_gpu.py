@@ -95,7 +95,7 @@ def paged_case(lens_q, starts, ps, hq, hkv, d, dt, seed=0):
     P = sum((x + ps - 1) // ps for x in kv) + 2
     perm = torch.randperm(P, generator=torch.Generator().manual_seed(seed)).tolist()
     bt = torch.full((S, maxp), -1, dtype=torch.int32)
-    tok_seq, pos, slots, cu, single, tile_seq, tile_start = [], [], [], [0], [], [], []
+    tok_seq, pos, slots, cu = [], [], [], [0]
     pi = 0
     for s in range(S):
         for lp in range((kv[s] + ps - 1) // ps):
@@ -106,28 +106,31 @@ def paged_case(lens_q, starts, ps, hq, hkv, d, dt, seed=0):
             pos.append(p)
             slots.append(int(bt[s, p // ps]) * ps + p % ps)
         cu.append(cu[-1] + lens_q[s])
-        if lens_q[s] == 1:
-            single.append(s)
-        else:
-            for q0 in range(0, lens_q[s], 64):
-                tile_seq.append(s)
-                tile_start.append(q0)
-    from simple_inference_b200.engine.batch import Workspace, pair_tiles
-    pairs = [0] * (len(tile_seq) + 2)
-    n_pairs = pair_tiles([starts[s] + min(q0 + 64, lens_q[s]) for s, q0 in zip(tile_seq, tile_start)], pairs)
-    wide = sorted(((starts[s] + min(q0 + 128, lens_q[s]), s, q0) for s in range(S)
-                   if lens_q[s] > 1 for q0 in range(0, lens_q[s], 128)), key=lambda w: -w[0])
+    from simple_inference_b200.engine.batch import Workspace
+    from simple_inference_b200.parts.attention_plan import plan_on_device
     I = lambda x: torch.tensor(x, dtype=torch.int32, device=dev())  # noqa: E731
     pool = torch.randn(P + 1, 2, hkv, ps, d, device=dev(), generator=g).to(dt)
     qkv = torch.randn(N, (hq + 2 * hkv) * d, device=dev(), generator=g).to(dt)
     ctx = types.SimpleNamespace(
         block_tables=[bt.to(dev())], tok_seq=I(tok_seq), positions=I(pos), cu_q=I(cu),
-        kv_slots=[I(slots)], single_seqs=I(single), n_single=len(single), tile_seq=I(tile_seq),
-        tile_start=I(tile_start), n_tiles=len(tile_seq), tile_pairs=I(pairs[:2 * n_pairs]),
-        n_pairs=n_pairs, wide_seq=I([w[1] for w in wide]), wide_start=I([w[2] for w in wide]),
-        n_wide=len(wide), max_kv_len=max(kv), max_q_len=max(lens_q), max_seqs=S,
-        ws=Workspace(dev(), N))
+        kv_slots=[I(slots)], max_kv_len=max(kv), max_q_len=max(lens_q), max_seqs=S,
+        ws=Workspace(dev(), N), plan=plan_on_device(lens_q, starts, dev()))
     return qkv, pool, ctx, N
+
+
+def assert_attention_close(out, ref, what=""):
+    """bfloat16 attention against float32 attention of the same bfloat16 inputs: the kernel
+    rounds P to bfloat16 before P V and the result once, so a row may differ by a few 2^-9 of
+    its own size.  The bound is relative to each row's RMS, which a wrong or missing key (a
+    dropped split, a window one key off) exceeds by far."""
+    out, ref = out.float(), ref.float()
+    assert bool(torch.isfinite(out).all()), f"{what}: not finite"
+    rms = ref.pow(2).mean(dim=-1, keepdim=True).sqrt()
+    worst = ((out - ref).abs() / (rms + 1e-6)).max()
+    assert worst < ATTENTION_REL_TOL, f"{what}: error {float(worst):.4f} of the row's RMS"
+
+
+ATTENTION_REL_TOL = 0.04
 
 
 @pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
@@ -233,12 +236,11 @@ def test_tensor_core_attention_bfloat16(ops, monkeypatch, what, lens, starts, ps
     if splits:
         monkeypatch.setattr(ops, "plan_kv_splits", lambda *a: splits)
     out = torch.zeros(n, hq * d, device=dev(), dtype=torch.bfloat16)
-    ops.paged_attention(qkv, pool, ctx, 0, out, hq, hkv, d, 1 / math.sqrt(d), window)
+    ops.paged_attention(qkv, pool, ctx, ctx.plan, 0, out, hq, hkv, d, 1 / math.sqrt(d), window)
     ref = torch.zeros(n, hq * d, device=dev())
     twin_ops.attention_generic(qkv.float(), pool.float(), ctx.block_tables[0], ctx.tok_seq,
                                ctx.positions, ref, hq, hkv, d, 1 / math.sqrt(d), window)
-    # the kernel rounds P to bfloat16 before P V and the result once: a few 1e-3 relative
-    assert (out.float() - ref).abs().max() < 2e-2
+    assert_attention_close(out, ref, what)
 
 
 WIDE_CASES = [
@@ -259,15 +261,15 @@ WIDE_CASES = [
 def test_tcgen05_prefill_attention(ops, what, lens, starts, ps, hq, hkv, window):
     d = 128
     qkv, pool, ctx, n = paged_case(lens, starts, ps, hq, hkv, d, torch.bfloat16, seed=3)
-    assert ops.wide_prefill_fits(ctx, d, ps)
+    assert ops.wide_prefill_fits(ctx.plan, d, ps)
     out = torch.zeros(n, hq * d, device=dev(), dtype=torch.bfloat16)
-    ops.attention_prefill_wide(qkv[:, :hq * d], pool, ctx, 0, out, hq, hkv, d, 1 / math.sqrt(d),
-                               window)
+    ops.attention_prefill_wide(qkv[:, :hq * d], pool, ctx, ctx.plan, 0, out, hq, hkv, d,
+                               1 / math.sqrt(d), window)
     ref = torch.zeros(n, hq * d, device=dev())
     twin_ops.attention_generic(qkv.float(), pool.float(), ctx.block_tables[0], ctx.tok_seq,
                                ctx.positions, ref, hq, hkv, d, 1 / math.sqrt(d), window)
     assert bool(torch.isfinite(out.float()).all()), "a bounded wait ran out (NaN marks it)"
-    assert (out.float() - ref).abs().max() < 2e-2
+    assert_attention_close(out, ref, what)
 
 
 def test_tcgen05_prefill_finds_one_far_key(ops):
@@ -288,7 +290,8 @@ def test_tcgen05_prefill_finds_one_far_key(ops):
             qkv[toks, h * d:(h + 1) * d] = key.bfloat16()
         pool[page, 1, :, off, :] = 7.0
     out = torch.zeros(n, hq * d, device=dev(), dtype=torch.bfloat16)
-    ops.attention_prefill_wide(qkv[:, :hq * d], pool, ctx, 0, out, hq, hkv, d, 1 / math.sqrt(d), None)
+    ops.attention_prefill_wide(qkv[:, :hq * d], pool, ctx, ctx.plan, 0, out, hq, hkv, d,
+                               1 / math.sqrt(d), None)
     assert (out.float() - 7.0).abs().max() < 0.1
 
 
@@ -312,8 +315,79 @@ def test_attention_finds_one_far_key_among_hundreds(ops):
                 qkv[toks, h * d:(h + 1) * d] = key.to(dt) * 1.0
             pool[page, 1, :, off, :] = 7.0
         out = torch.zeros(n, hq * d, device=dev(), dtype=dt)
-        ops.paged_attention(qkv, pool, ctx, 0, out, hq, hkv, d, 1 / math.sqrt(d), None)
+        ops.paged_attention(qkv, pool, ctx, ctx.plan, 0, out, hq, hkv, d, 1 / math.sqrt(d), None)
         assert (out.float() - 7.0).abs().max() < 0.1, f"{dt}: the far key was not found"
+
+
+def _plant_key(qkv, pool, ctx, seq, far, hq, hkv, d, ps, dt):
+    """Make key `far` of sequence `seq` match every query of that sequence 30 times better than
+    any other key, and give it the value 7."""
+    table = ctx.block_tables[0]
+    page, off = int(table[seq, far // ps]), far % ps
+    toks = (ctx.tok_seq == seq).nonzero().flatten()
+    for h in range(hq):
+        kvh = h // (hq // hkv)
+        key = torch.zeros(d, device=dev())
+        key[h * 3] = 30.0
+        pool[page, 0, kvh, off, h * 3] = 30.0
+        qkv[toks, h * d:(h + 1) * d] = key.to(dt)
+    pool[page, 1, :, off, :] = 7.0
+
+
+@pytest.mark.parametrize("splits", [7, 32])
+def test_split_decode_attention_finds_one_far_key(ops, monkeypatch, splits):
+    """The TMA-fed decode kernel at head size 128 with its keys cut into 7 and 32 splits: the
+    one key that matters lies in one split, and the join must weigh that split's part."""
+    hq, hkv, d, ps = 24, 8, 128, 16
+    monkeypatch.setattr(ops, "plan_kv_splits", lambda *a: splits)
+    for fars in ((437, 23), (2040, 1000), (0, 1999)):
+        qkv, pool, ctx, n = paged_case([1, 1], [2047, 2000], ps, hq, hkv, d, torch.bfloat16, seed=7)
+        pool.mul_(0.05)
+        for seq, far in enumerate(fars):
+            _plant_key(qkv, pool, ctx, seq, far, hq, hkv, d, ps, torch.bfloat16)
+        out = torch.zeros(n, hq * d, device=dev(), dtype=torch.bfloat16)
+        ops.paged_attention(qkv, pool, ctx, ctx.plan, 0, out, hq, hkv, d, 1 / math.sqrt(d), None)
+        assert (out.float() - 7.0).abs().max() < 0.1, f"keys {fars} with {splits} splits"
+
+
+WINDOW_EDGE_CASES = [
+    # what, head size, page, window, (start, tokens) of the sequences, position of the planted key
+    ("decode by TMA, head 128", 128, 16, 40, [(139, 1), (140, 1)], 100),
+    ("decode by TMA, window over many tiles", 128, 16, 300, [(1299, 1), (1300, 1)], 1000),
+    ("decode, head 48", 48, 8, 50, [(249, 1), (250, 1)], 200),
+    ("mma.sync portions, head 64", 64, 16, 40, [(120, 70)], 100),
+    ("mma.sync portions, window over a tile edge", 32, 16, 70, [(130, 100)], 100),
+    ("tcgen05 portions, head 128", 128, 16, 40, [(100, 200)], 130),
+    ("tcgen05 portions, window over several tiles", 128, 16, 300, [(900, 260)], 700),
+]
+
+
+@pytest.mark.parametrize("what,d,ps,window,seqs,far", WINDOW_EDGE_CASES,
+                         ids=[c[0] for c in WINDOW_EDGE_CASES])
+def test_the_window_ends_exactly_where_it_should(ops, what, d, ps, window, seqs, far):
+    """A query at position p sees the keys at p-window+1 .. p.  One key matches every query
+    30 times better than the rest and carries the value 7: rows whose window still holds it
+    must return 7, rows whose window has just passed it must not see it at all.  Random keys
+    would hide an edge that is off by one (one key among `window` moves a row by 1/window)."""
+    hq, hkv = 4, 2
+    lens, starts = [n for _, n in seqs], [s for s, _ in seqs]
+    qkv, pool, ctx, n = paged_case(lens, starts, ps, hq, hkv, d, torch.bfloat16, seed=9)
+    pool.mul_(0.05)
+    for seq in range(len(seqs)):
+        _plant_key(qkv, pool, ctx, seq, far, hq, hkv, d, ps, torch.bfloat16)
+    out = torch.zeros(n, hq * d, device=dev(), dtype=torch.bfloat16)
+    ops.paged_attention(qkv, pool, ctx, ctx.plan, 0, out, hq, hkv, d, 1 / math.sqrt(d), window)
+    pos = ctx.positions.tolist()
+    sees = torch.tensor([far <= p <= far + window - 1 for p in pos], device=dev())
+    assert bool(sees.any()) and bool((~sees).any()), "the case must have rows on both sides"
+    err = (out.float() - 7.0).abs().amax(dim=-1)
+    assert float(err[sees].max()) < 0.1, "a row whose window holds the key did not find it"
+    assert float(out.float().abs().amax(dim=-1)[~sees].max()) < 1.0, \
+        "a row whose window has passed the key still saw it"
+    ref = torch.zeros(n, hq * d, device=dev())
+    twin_ops.attention_generic(qkv.float(), pool.float(), ctx.block_tables[0], ctx.tok_seq,
+                               ctx.positions, ref, hq, hkv, d, 1 / math.sqrt(d), window)
+    assert (out.float() - ref).abs().max() < 2e-2
 
 
 def test_sampling_kernel_against_plain_sampler(ops):

@@ -17,14 +17,16 @@ class Harness:
     """A cache, a batch builder and a workspace around parts under test."""
 
     def __init__(self, specs, dtype, page_size=4, pages=80, max_tokens=256, max_seqs=4,
-                 max_seq_len=256):
+                 max_seq_len=256, parts=()):
         from simple_inference_b200.cache import CacheManager
         from simple_inference_b200.engine.batch import BatchBuilder, Workspace
         from simple_inference_b200.parts import Runtime
         self.rt = Runtime(torch.device(DEV), dtype)
         # a request brings at most 64 tokens per step; a batch may hold max_tokens in all
         self.cache = CacheManager(specs, page_size, pages, max_seqs, 64, dtype, DEV)
-        self.builder = BatchBuilder(self.cache, max_tokens, max_seqs, max_seq_len, self.rt.device)
+        planners = {cls.name: cls for part in parts for cls in part.step_planners()}
+        self.builder = BatchBuilder(self.cache, max_tokens, max_seqs, max_seq_len, self.rt.device,
+                                    planners=planners)
         self.ws = Workspace(self.rt.device, max_tokens)
         self.views = self.cache.layer_caches()
 
@@ -93,7 +95,7 @@ def test_attention_part_in_portions_and_with_a_window(dtype, window):
         "hidden_size": H, "num_heads": hq, "num_kv_heads": hkv, "head_dim": d, "window": window,
         "position": PartSpec("rope", {"head_dim": d, "theta": 1000.0, "scaling": scaling})}))
     assert mixer.cache_spec().window == window
-    h = Harness([mixer.cache_spec()], dtype, page_size=4, pages=40 if window else 80)
+    h = Harness([mixer.cache_spec()], dtype, page_size=4, pages=40 if window else 80, parts=[mixer])
     ws = {n: rnd(*s.shape, seed=i, scale=0.2).to(dtype) for i, (n, s) in enumerate(mixer.tensors().items())}
     mixer.bind({n: t.to(DEV) for n, t in ws.items()}, h.rt)
     cfg = {"num_attention_heads": hq, "num_key_value_heads": hkv, "head_dim": d}

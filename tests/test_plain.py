@@ -116,3 +116,47 @@ def test_uniform_of_every_hash_lies_strictly_inside_the_unit_interval():
         noise = -np.log(-np.log(u, dtype=np.float32), dtype=np.float32)
         assert np.isfinite(noise).all()
     assert np.isfinite(plain_llama.gumbel_noise(3, 1, 2, 200_000).numpy()).all()
+
+
+@pytest.mark.parametrize("name", ["A", "B", "D"])
+def test_one_wrong_key_moves_the_logits_by_more_than_the_bfloat16_tolerance(name, tmp_path):
+    """The point of a tolerance: a fault must not fit under it.  Take the key and value of one
+    token from another token, in one layer, and the logits of the plain model move by more
+    than the bound that the bfloat16 replay tests allow between engine and plain model."""
+    from tests.conftest import TINY
+    from tests.test_replay_gpu import TOL
+    write_random_model(tmp_path, TINY[name], seed=11 + "ABCD".index(name))
+    cfg, w = plain_llama.read_folder(tmp_path)
+    ids = random_ids(97, cfg["vocab_size"], 101)
+    base = plain_llama.forward(cfg, w, ids)
+    plain_attention = plain_llama.attention
+    try:
+        for layer in range(cfg["num_hidden_layers"]):
+            for wrong, taken_from in ((10, 50), (40, 3)):
+                calls = [0]
+
+                def with_one_wrong_key(q, k, v, positions, window=None, scale=None):
+                    if calls[0] == layer:
+                        k, v = k.clone(), v.clone()
+                        k[wrong], v[wrong] = k[taken_from], v[taken_from]
+                    calls[0] += 1
+                    return plain_attention(q, k, v, positions, window, scale)
+
+                plain_llama.attention = with_one_wrong_key
+                moved = float((plain_llama.forward(cfg, w, ids) - base).abs().max())
+                assert moved > 1.2 * TOL["bfloat16"], (layer, wrong, moved)
+    finally:
+        plain_llama.attention = plain_attention
+
+
+def test_sampling_filters_keep_what_the_reference_keeps():
+    """golden_sampling.json holds which entries the reference's own filter_top_k and
+    filter_top_p (sampling.py:69-128, after its division by the temperature, :39-52) leave
+    finite, for rows with ties at the top and across the k-th place and for a peaked row."""
+    rec = json.loads((GOLDEN / "golden_sampling.json").read_text())
+    rows = torch.tensor(rec["rows"])
+    for (temperature, top_k, top_p), per_row in zip(rec["settings"], rec["reference_kept"]):
+        for row, want in zip(rows, per_row):
+            z = plain_llama.filter_logits(row, temperature, int(top_k), top_p)
+            assert torch.isfinite(z).nonzero().flatten().tolist() == want, (temperature, top_k, top_p)
+            assert torch.equal(z[want], (row / temperature)[want])

@@ -17,11 +17,17 @@ from tests.replay_util import Trace
 
 pytestmark = pytest.mark.gpu
 
-# tolerances on logits whose magnitude is about 1: float32 differs from the plain
-# model by summation order only; bfloat16 by the rounding of activations.
-TOL = {"float32": 2e-5, "bfloat16": 4e-2}
+# Tolerances on logits whose standard deviation is 0.2 to 0.3: float32 differs from the plain
+# model by summation order only; bfloat16 by the rounding of activations, measured at up to
+# 7.5e-3 over all configurations and cuts but the sharpened Tiny D, and allowed twice that.
+# One key and value taken from a wrong token in one layer moves these logits by 0.019 to 0.9
+# (tests/test_plain.py proves it on the CPU), so it cannot hide under the bound.
+TOL = {"float32": 2e-5, "bfloat16": 1.5e-2}
+# Sharpened Tiny D: scores 36 times larger make the softmax of its 128-wide heads feel every
+# rounding of q and k (measured 0.053 to 0.062); a wrong key moves its logits by 0.34 and more.
+TOL_SHARP_D = {"float32": 2e-5, "bfloat16": 0.15}
 # between two ways of cutting the same request in the same dtype
-CUT_TOL = {"float32": 2e-6, "bfloat16": 3e-2}
+CUT_TOL = {"float32": 2e-6, "bfloat16": 1.5e-2}
 
 
 @pytest.fixture(scope="module")
@@ -38,10 +44,20 @@ def cases(model_folders, tmp_path_factory):
             t[k] = (t[k].float() * 6.0).to(t[k].dtype)
     save_file(t, str(sharp / "model.safetensors"))
     folders["sharp"] = sharp
+    # the same for Tiny D, whose head size of 128 and long prompts take the tcgen05 attention,
+    # the TMA-fed decode attention and the tcgen05 products
+    sharp_d = tmp_path_factory.mktemp("tiny_sharp_d")
+    write_random_model(sharp_d, TINY["D"], seed=23)
+    t = load_file(str(sharp_d / "model.safetensors"))
+    for k in list(t):
+        if "q_proj" in k or "k_proj" in k:
+            t[k] = (t[k].float() * 6.0).to(t[k].dtype)
+    save_file(t, str(sharp_d / "model.safetensors"))
+    folders["sharpD"] = sharp_d
     out = {}
     for name, folder in folders.items():
         cfg, w = plain_llama.read_folder(folder)
-        top = min(cfg["max_position_embeddings"], 420 if name == "D" else 230)
+        top = min(cfg["max_position_embeddings"], 420 if name in ("D", "sharpD") else 230)
         lens = [top, 97, 64, 33, 5, 150][: 6 if top > 128 else 5]
         lens = [min(n, top) for n in lens]
         seqs = [random_ids(n, cfg["vocab_size"], 100 + i) for i, n in enumerate(lens)]
@@ -49,16 +65,21 @@ def cases(model_folders, tmp_path_factory):
     return out
 
 
+def _tol(table, dtype, what):
+    return TOL_SHARP_D[dtype] if what.startswith("sharpD") else table[dtype]
+
+
 def _check(got, want, dtype, what):
     diff = (got - want).abs().max().item()
-    assert diff < TOL[dtype], f"{what}: max |engine - plain| = {diff}"
+    print(f"max |engine - plain| {dtype} {what}: {diff:.2e}")     # shown by pytest -rA
+    assert diff < _tol(TOL, dtype, what), f"{what}: max |engine - plain| = {diff}"
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D", "sharp"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "sharp", "sharpD"])
 def test_whole_then_last_32_then_portions(name, dtype, cases, tmp_path):
     folder, cfg, w, seqs, plain = cases[name]
-    with Trace(folder, dtype, tmp_path, max_tokens=512 if name == "D" else 256) as tr:
+    with Trace(folder, dtype, tmp_path, max_tokens=512 if "D" in name else 256) as tr:
         for i, (ids, ref) in enumerate(zip(seqs[:3], plain[:3])):
             n = len(ids)
             # (1) alone and whole, every position wanted
@@ -71,7 +92,7 @@ def test_whole_then_last_32_then_portions(name, dtype, cases, tmp_path):
                 rows.append(tr.step([(f"d{i}", [ids[p]], [0])], end=[f"d{i}"] if p == n - 1 else []))
             tail = torch.cat(rows)
             _check(tail, ref[head - 1:], dtype, f"{name} seq {i} last 32 one by one")
-            assert (tail - whole[head - 1:]).abs().max() < CUT_TOL[dtype]
+            assert (tail - whole[head - 1:]).abs().max() < _tol(CUT_TOL, dtype, name)
             # (3) portions of changing size, down to two tokens
             sizes, p, rows = [7, 2, 13, 3, 2, 31, 2, 5, 64, 2, 9], 0, []
             k = 0
@@ -83,29 +104,33 @@ def test_whole_then_last_32_then_portions(name, dtype, cases, tmp_path):
                 k += 1
             parts = torch.cat(rows)
             _check(parts, ref, dtype, f"{name} seq {i} in portions")
-            assert (parts - whole).abs().max() < CUT_TOL[dtype]
+            assert (parts - whole).abs().max() < _tol(CUT_TOL, dtype, name)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "sharp"])
+@pytest.mark.parametrize("name", ["A", "B", "sharp", "D", "sharpD"])
 def test_mixed_batches_with_pages_used_again(name, dtype, cases, tmp_path):
     """Up to four live requests, portions of some beside decoded tokens of others, in a pool
-    of 320 tokens (20 pages) that the requests need 2.5 times over."""
+    of 320 tokens (20 pages) that the requests need 2.5 times over.  The configurations with
+    heads of 128 get longer prompts, a pool of 640 tokens that they need 1.5 times over, and
+    portions of 64, 128 and 200 tokens, so that the tcgen05 attention and products run beside
+    decoded tokens of other requests while pages change hands."""
     folder, cfg, w, seqs, plain = cases[name]
     lens = [len(s) for s in seqs]
-    assert sum((n + 63) // 64 * 64 for n in lens) > 320      # more than the pool: pages come back
+    pool = 640 if "D" in name else 320
+    assert sum((n + 63) // 64 * 64 for n in lens) > pool     # more than the pool: pages come back
     # each request: a prompt part fed in portions, then the rest token by token
     plan = {i: {"prompt": max(2, n - 20 - 3 * i), "fed": 0} for i, n in enumerate(lens)}
-    portion = [9, 2, 30, 5, 17, 2, 64]
+    portion = [9, 2, 200, 5, 128, 2, 64] if "D" in name else [9, 2, 30, 5, 17, 2, 64]
     waiting = list(range(len(seqs)))
     live: list[int] = []
     got = {i: {} for i in range(len(seqs))}
-    with Trace(folder, dtype, tmp_path, max_tokens=320) as tr:
+    with Trace(folder, dtype, tmp_path, max_tokens=pool) as tr:
         k = 0
         while waiting or live:
             # admit while at most four are live and the rounded-up lengths fit in the pool
             while waiting and len(live) < 4 and \
-                    sum((lens[j] + 63) // 64 * 64 for j in live + [waiting[0]]) <= 320:
+                    sum((lens[j] + 63) // 64 * 64 for j in live + [waiting[0]]) <= pool:
                 live.append(waiting.pop(0))
             entries, ending, index = [], [], []
             for i in live:

@@ -101,8 +101,8 @@ def define_toy():
             hidden_size=cfg.hidden_size, vocab_size=cfg.vocab_size, layers=layers,
             run_order=ModelPlan.sequential(len(layers)),
             final_norm=PartSpec("rmsnorm", {"hidden_size": cfg.hidden_size, "eps": cfg.rms_norm_eps}),
-            tie_embeddings=cfg.tie_word_embeddings, embedding_name="model.embed_tokens.weight",
-            final_norm_names={"weight": "model.norm.weight"}, head_name="lm_head.weight",
+            tie_embeddings=cfg.tie_word_embeddings, embedding_names={"weight": "model.embed_tokens.weight"},
+            final_norm_names={"weight": "model.norm.weight"}, head_names={"weight": "lm_head.weight"},
             max_positions=cfg.max_position_embeddings)
 
     register_architecture("ToyForCausalLM", ToyConfig, toy_plan)
@@ -292,8 +292,8 @@ def define_routed():
         return ModelPlan(
             hidden_size=cfg.hidden_size, vocab_size=cfg.vocab_size, layers=layers, run_order=order,
             final_norm=norm, tie_embeddings=cfg.tie_word_embeddings,
-            embedding_name="model.embed_tokens.weight",
-            final_norm_names={"weight": "model.norm.weight"}, head_name="lm_head.weight",
+            embedding_names={"weight": "model.embed_tokens.weight"},
+            final_norm_names={"weight": "model.norm.weight"}, head_names={"weight": "lm_head.weight"},
             max_positions=cfg.max_position_embeddings)
 
     register_architecture("RoutedToyForCausalLM", RoutedConfig, routed_plan)
@@ -362,4 +362,331 @@ def test_routed_feed_forward_another_norm_and_a_layer_run_twice(tmp_path):
             o += n
             fed[i] += n
     for i in range(2):
+        assert (torch.cat(got[i]) - want[i]).abs().max() < 3e-5, f"sequence {i}"
+
+
+# --------------------------------------------------------------------------------------
+# A state mixer that a CUDA graph can hold: decode steps replay from a graph that is
+# captured inside a live step, and the state must advance exactly once per step.
+# --------------------------------------------------------------------------------------
+
+def define_graph_toy():
+    from simple_inference_b200 import ops
+    from simple_inference_b200.config import register_architecture
+    from simple_inference_b200.config.model_config import LlamaConfig
+    from simple_inference_b200.models.llama import llama_layer_plan
+    from simple_inference_b200.models.plan import LayerPlan, ModelPlan
+    from simple_inference_b200.parts import Mixer, PartSpec, StateSpec, TensorSpec, register_mixer
+
+    @register_mixer("toy_decay_on_device")
+    class DeviceDecayMixer(Mixer):
+        """s <- decay * s + x_t, y_t = W s, with single-token steps done by device-side index
+        arithmetic alone (no read-back), so that they can be recorded in a CUDA graph."""
+
+        def __init__(self, hidden_size: int, decay: float):
+            self.hidden_size, self.decay = hidden_size, decay
+
+        def tensors(self):
+            return {"w": TensorSpec((self.hidden_size, self.hidden_size))}
+
+        def cache_spec(self):
+            return StateSpec((self.hidden_size,), "float32")
+
+        def bind(self, tensors, rt):
+            super().bind(tensors, rt)
+            self.w = tensors["w"]
+
+        def forward(self, x, ctx, cache):
+            out = ctx.ws.get("toy.out", (x.shape[0], self.hidden_size), x.dtype)
+            if ctx.max_q_len == 1:          # one token per sequence: rows of x are sequences
+                idx = ctx.seq_slots.long()
+                new = cache.state[idx] * self.decay + x.float()
+                cache.state.index_copy_(0, idx, new)   # padding rows all hit the scratch slot
+                return ops.linear(new.to(x.dtype), self.w, out)
+            sums = torch.empty(x.shape, dtype=torch.float32, device=x.device)
+            slots = ctx.seq_slots.tolist()
+            t = 0
+            for s, n in enumerate(ctx.q_lens):
+                state = cache.state[slots[s]]
+                for i in range(n):
+                    state.mul_(self.decay).add_(x[t + i].float())
+                    sums[t + i] = state
+                t += n
+            return ops.linear(sums.to(x.dtype), self.w, out)
+
+    @dataclass(kw_only=True)
+    class GraphToyConfig(LlamaConfig):
+        decay: float = 0.5
+
+    def plan(cfg: GraphToyConfig) -> ModelPlan:
+        layers = []
+        for i in range(cfg.num_hidden_layers):
+            lp = llama_layer_plan(cfg, i)
+            params, names = dict(lp.block.params), lp.tensor_names
+            if i % 2 == 1:
+                params["mixer"] = PartSpec("toy_decay_on_device", {"hidden_size": cfg.hidden_size,
+                                                                   "decay": cfg.decay})
+                names = {k: v for k, v in names.items() if not k.startswith("mixer.")}
+                names["mixer.w"] = f"model.layers.{i}.toy.w"
+            layers.append(LayerPlan(PartSpec("prenorm", params), names))
+        return ModelPlan(
+            hidden_size=cfg.hidden_size, vocab_size=cfg.vocab_size, layers=layers,
+            run_order=ModelPlan.sequential(len(layers)),
+            final_norm=PartSpec("rmsnorm", {"hidden_size": cfg.hidden_size, "eps": cfg.rms_norm_eps}),
+            tie_embeddings=True, embedding_names={"weight": "model.embed_tokens.weight"},
+            final_norm_names={"weight": "model.norm.weight"}, head_names={"weight": "lm_head.weight"},
+            max_positions=cfg.max_position_embeddings)
+
+    register_architecture("GraphToyForCausalLM", GraphToyConfig, plan)
+
+
+def test_state_mixer_in_bfloat16_with_graphs_captured_inside_a_live_step(tmp_path):
+    """Decode steps of a model with a state mixer, replayed from CUDA graphs that are captured
+    when their batch size is first met (no warm-up): the logits must equal those of the same
+    steps run without graphs.  A capture that ran the live step more than once would advance
+    the state more than once and part from the eager run at the first graph step."""
+    define_graph_toy()
+    from simple_inference_b200 import load_model, write_random_model
+    from simple_inference_b200.cache import CacheManager
+    from simple_inference_b200.engine import ModelRunner, StepEntry
+    config = {
+        "architectures": ["GraphToyForCausalLM"], "num_hidden_layers": 4, "hidden_size": 64,
+        "num_attention_heads": 4, "num_key_value_heads": 2, "head_dim": 16,
+        "intermediate_size": 96, "vocab_size": 120, "rope_theta": 10000.0, "rms_norm_eps": 1e-5,
+        "tie_word_embeddings": True, "max_position_embeddings": 128, "torch_dtype": "bfloat16",
+        "decay": 0.8,
+    }
+    write_random_model(tmp_path, config, seed=6)
+    _, model = load_model(tmp_path, "bfloat16", DEV)
+    seqs = [random_ids(n, 120, 70 + n) for n in (30, 22, 17)]
+
+    def run(graphs: bool):
+        cache = CacheManager(model.cache_specs(), 4, 60, 4, 64, torch.bfloat16, DEV)
+        runner = ModelRunner(model, cache, model.rt, 64, 4, 128, cuda_graphs=graphs)
+        out = []
+        for i in range(3):
+            cache.admit(i, 40)
+        runner.step([StepEntry(i, seqs[i][:10], []) for i in range(3)])        # prompts
+        for t in range(10, 17):                                                # three decoding
+            out.append(runner.step([StepEntry(i, [seqs[i][t]], [0]) for i in range(3)]).clone())
+        cache.release(2)
+        for t in range(17, 22):                                                # two: another bucket
+            out.append(runner.step([StepEntry(i, [seqs[i][t]], [0]) for i in range(2)]).clone())
+        if graphs:
+            assert sorted(runner._graphs) == [2, 4], "both buckets were captured on the way"
+        return torch.cat(out).float().cpu()
+
+    eager, replayed = run(False), run(True)
+    assert torch.isfinite(eager).all()
+    # the same kernels on the same numbers but for the number of key splits, which a graph plans
+    # for the longest context: a rounding apart at most; a state advanced twice is far off
+    assert (eager - replayed).abs().max() < 2e-2 * float(eager.abs().max())
+
+
+# --------------------------------------------------------------------------------------
+# A cache that is one vector per token in pages of its own size, an embedding with a
+# scale and a head with a cap: registered kinds, no framework file touched.
+# --------------------------------------------------------------------------------------
+
+def define_latent_toy():
+    from simple_inference_b200 import ops
+    from simple_inference_b200.config import register_architecture
+    from simple_inference_b200.config.model_config import LlamaConfig
+    from simple_inference_b200.models.llama import llama_layer_plan
+    from simple_inference_b200.models.plan import LayerPlan, ModelPlan
+    from simple_inference_b200.parts import (Embedding, Head, Mixer, PartSpec, TensorSpec,
+                                             register_embedding, register_head, register_mixer)
+
+    @dataclass(frozen=True)
+    class LatentSpec:
+        """One vector of `width` numbers per token, in pages of 8 tokens whatever the engine's
+        page size: a cache kind the framework has never heard of."""
+        width: int
+        window: int | None = None
+        page_size: int | None = 8
+        storage = "pages"
+
+        def page_shape(self, page_size):
+            return (page_size, self.width)
+
+    @register_mixer("toy_latent_mean")
+    class LatentMeanMixer(Mixer):
+        """c_t = Wc x_t is stored per token; y_t = Wo * mean of c_j over the request's j <= t."""
+
+        def __init__(self, hidden_size: int, width: int):
+            self.hidden_size, self.width = hidden_size, width
+
+        def tensors(self):
+            return {"wc": TensorSpec((self.width, self.hidden_size)),
+                    "wo": TensorSpec((self.hidden_size, self.width))}
+
+        def cache_spec(self):
+            return LatentSpec(self.width)
+
+        def bind(self, tensors, rt):
+            super().bind(tensors, rt)
+            self.wc, self.wo = tensors["wc"], tensors["wo"]
+
+        def forward(self, x, ctx, cache):
+            n = x.shape[0]
+            c = torch.empty(n, self.width, dtype=x.dtype, device=x.device)
+            ops.linear(x, self.wc, c)
+            flat = cache.pool.view(-1, self.width)            # [(pages+1) * page_size, width]
+            flat[ctx.kv_slots[cache.group].long()] = c
+            table = ctx.block_tables[cache.group].tolist()
+            means = torch.empty_like(c)
+            t = 0
+            for s, (q, kv) in enumerate(zip(ctx.q_lens, ctx.kv_lens)):
+                rows = torch.tensor([table[s][j // cache.page_size] * cache.page_size
+                                     + j % cache.page_size for j in range(kv)], device=x.device)
+                run = flat[rows].float().cumsum(0) / torch.arange(1, kv + 1, device=x.device)[:, None]
+                means[t:t + q] = run[kv - q:].to(x.dtype)
+                t += q
+            out = ctx.ws.get("toy.latent_out", (n, self.hidden_size), x.dtype)
+            return ops.linear(means, self.wo, out)
+
+    @register_embedding("toy_scaled_embedding")
+    class ScaledEmbedding(Embedding):
+        def __init__(self, vocab_size: int, hidden_size: int, scale: float):
+            self.v, self.h, self.scale = vocab_size, hidden_size, scale
+
+        def tensors(self):
+            return {"weight": TensorSpec((self.v, self.h))}
+
+        def bind(self, tensors, rt):
+            super().bind(tensors, rt)
+            self.weight = tensors["weight"]
+
+        def forward(self, token_ids, ctx):
+            residual = ctx.ws.get("residual", (token_ids.shape[0], self.h), torch.float32)
+            ops.embed_gather(self.weight, token_ids, residual)
+            return residual.mul_(self.scale)
+
+        def output_matrix(self):
+            return self.weight
+
+    @register_head("toy_capped_head")
+    class CappedHead(Head):
+        """logits = cap * tanh(x E^T / cap) + bias, with the embedding's matrix."""
+
+        def __init__(self, vocab_size: int, hidden_size: int, cap: float):
+            self.v, self.h, self.cap = vocab_size, hidden_size, cap
+
+        def tensors(self):
+            return {"bias": TensorSpec((self.v,), kind="vector", init="normal")}
+
+        def bind(self, tensors, rt, embedding=None):
+            super().bind(tensors, rt, embedding)
+            self.weight, self.bias = embedding.output_matrix(), tensors["bias"]
+
+        def forward(self, x, ctx):
+            logits = ctx.ws.get("logits", (x.shape[0], self.v), torch.float32,
+                                row_cap=ctx.ws.max_logit_rows)
+            ops.linear(x, self.weight, logits)
+            return torch.tanh(logits / self.cap) * self.cap + self.bias.float()
+
+    @dataclass(kw_only=True)
+    class LatentToyConfig(LlamaConfig):
+        latent_width: int = 12
+        embedding_scale: float = 3.0
+        logit_cap: float = 2.0
+
+    def plan(cfg: LatentToyConfig) -> ModelPlan:
+        layers = []
+        for i in range(cfg.num_hidden_layers):
+            lp = llama_layer_plan(cfg, i)
+            params, names = dict(lp.block.params), lp.tensor_names
+            if i % 2 == 1:
+                params["mixer"] = PartSpec("toy_latent_mean", {"hidden_size": cfg.hidden_size,
+                                                               "width": cfg.latent_width})
+                names = {k: v for k, v in names.items() if not k.startswith("mixer.")}
+                names["mixer.wc"] = f"model.layers.{i}.latent.wc"
+                names["mixer.wo"] = f"model.layers.{i}.latent.wo"
+            layers.append(LayerPlan(PartSpec("prenorm", params), names))
+        return ModelPlan(
+            hidden_size=cfg.hidden_size, vocab_size=cfg.vocab_size, layers=layers,
+            run_order=ModelPlan.sequential(len(layers)),
+            final_norm=PartSpec("rmsnorm", {"hidden_size": cfg.hidden_size, "eps": cfg.rms_norm_eps}),
+            tie_embeddings=True,
+            embedding=PartSpec("toy_scaled_embedding", {
+                "vocab_size": cfg.vocab_size, "hidden_size": cfg.hidden_size,
+                "scale": cfg.embedding_scale}),
+            head=PartSpec("toy_capped_head", {"vocab_size": cfg.vocab_size,
+                                              "hidden_size": cfg.hidden_size, "cap": cfg.logit_cap}),
+            embedding_names={"weight": "model.embed_tokens.weight"},
+            final_norm_names={"weight": "model.norm.weight"}, head_names={"bias": "lm_head.bias"},
+            max_positions=cfg.max_position_embeddings)
+
+    register_architecture("LatentToyForCausalLM", LatentToyConfig, plan)
+
+
+def plain_latent(cfg, w, ids):
+    from tests import plain_llama as pl
+    eps = cfg["rms_norm_eps"]
+    x = w["model.embed_tokens.weight"][torch.tensor(ids)] * cfg["embedding_scale"]
+    pos = list(range(len(ids)))
+    freqs = pl.rope_frequencies(pl.head_dim_of(cfg), cfg["rope_theta"], None)
+    for i in range(cfg["num_hidden_layers"]):
+        p = f"model.layers.{i}."
+        h = pl.rmsnorm(x, w[p + "input_layernorm.weight"], eps)
+        if i % 2 == 1:
+            c = h @ w[p + "latent.wc"].T
+            mean = c.cumsum(0) / torch.arange(1, len(ids) + 1)[:, None]
+            x = x + mean @ w[p + "latent.wo"].T
+        else:
+            x = x + pl.attention_layer(h, w, p + "self_attn.", cfg, pos, freqs)
+        x = x + pl.mlp(pl.rmsnorm(x, w[p + "post_attention_layernorm.weight"], eps), w, p + "mlp.")
+    logits = pl.rmsnorm(x, w["model.norm.weight"], eps) @ w["model.embed_tokens.weight"].T
+    return torch.tanh(logits / cfg["logit_cap"]) * cfg["logit_cap"] + w["lm_head.bias"]
+
+
+def test_a_latent_cache_in_pages_of_its_own_a_scaled_embedding_and_a_capped_head(tmp_path):
+    define_latent_toy()
+    from simple_inference_b200 import load_model, write_random_model
+    from simple_inference_b200.cache import CacheManager
+    from simple_inference_b200.engine import ModelRunner, StepEntry
+    from tests import plain_llama
+    config = {
+        "architectures": ["LatentToyForCausalLM"], "num_hidden_layers": 4, "hidden_size": 40,
+        "num_attention_heads": 2, "num_key_value_heads": 1, "head_dim": 16,
+        "intermediate_size": 56, "vocab_size": 90, "rope_theta": 10000.0, "rms_norm_eps": 1e-5,
+        "tie_word_embeddings": True, "max_position_embeddings": 128, "torch_dtype": "float32",
+        "latent_width": 12, "embedding_scale": 3.0, "logit_cap": 2.0,
+    }
+    write_random_model(tmp_path, config, seed=8)
+    cfg, model = load_model(tmp_path, "float32", DEV)
+    specs = model.cache_specs()
+    assert [s.storage for s in specs] == ["pages"] * 4 and specs[0] != specs[1]
+    # attention pages of 4 tokens (the manager's size), latent pages of 8 (their own): 16 and 9
+    # pages hold 64 and 72 tokens, fewer than the 86 the three requests need together
+    cache = CacheManager(specs, 4, {0: 16, 1: 9}, 2, 64, torch.float32, DEV)
+    assert [g.page_size for g in cache.groups] == [4, 8]
+    assert tuple(cache.groups[1].pool.shape) == (2, 10, 8, 12)
+    runner = ModelRunner(model, cache, model.rt, 64, 2, 128, max_logit_rows=64)
+    pcfg, w = plain_llama.read_folder(tmp_path)
+    seqs = [random_ids(n, 90, 50 + n) for n in (41, 26, 19)]
+    want = [plain_latent(pcfg, w, s) for s in seqs]
+    got = {i: [] for i in range(3)}
+    fed = {i: 0 for i in range(3)}
+
+    def feed(step):
+        entries = [StepEntry(i, seqs[i][fed[i]:fed[i] + n], list(range(n))) for i, n in step]
+        out = runner.step(entries).clone().cpu()
+        o = 0
+        for i, n in step:
+            got[i].append(out[o:o + n])
+            o += n
+            fed[i] += n
+        cache.check()
+
+    cache.admit(0, 28)
+    cache.admit(1, 26)
+    for step in ([(0, 13)], [(0, 1), (1, 9)], [(1, 17), (0, 2)], [(0, 12)]):
+        feed(step)
+    cache.release(1)                 # its pages of both sizes go to request 2
+    cache.admit(2, 19)
+    cache.reserve_to(0, 41)
+    for step in ([(2, 3), (0, 1)], [(2, 16), (0, 12)]):
+        feed(step)
+    for i in range(3):
         assert (torch.cat(got[i]) - want[i]).abs().max() < 3e-5, f"sequence {i}"

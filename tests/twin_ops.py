@@ -95,7 +95,7 @@ def attention_generic(q, pool, block_table, tok_seq, positions, out, num_q_heads
     return out
 
 
-def paged_attention(q, pool, ctx, group, out, num_q_heads, num_kv_heads, head_dim, scale, window):
+def paged_attention(q, pool, ctx, plan, group, out, num_q_heads, num_kv_heads, head_dim, scale, window):
     return attention_generic(q, pool, ctx.block_tables[group], ctx.tok_seq, ctx.positions, out,
                              num_q_heads, num_kv_heads, head_dim, scale, window)
 
