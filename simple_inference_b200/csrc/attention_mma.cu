@@ -771,28 +771,62 @@ attn_decode_tma_kernel(const __grid_constant__ CUtensorMap pool_map, const bf16*
 }
 
 // grid (sequences with one token, query heads); joins the splits' partial results.
+// Every load of the partial results is issued before anything waits on one: a lane per split
+// fetches (m, l) and the weights exp2(m - max) are formed by warp shuffles; then each thread
+// sums its column over the splits eight loads at a time.
+constexpr int MERGE_MAX_SPLITS = 64;
 __global__ void attn_merge_kernel(const float* __restrict__ part_acc,
                                   const float* __restrict__ part_ml,
                                   const int* __restrict__ cu_q,
                                   const int* __restrict__ single_seqs, bf16* __restrict__ out,
                                   int out_stride, int n_q_heads, int n_splits) {
+  __shared__ float weight[MERGE_MAX_SPLITS];
+  __shared__ float inv_l;
+  const int head = blockIdx.y;
+  const int tok = cu_q[single_seqs[blockIdx.x]];   // not written by any kernel of the step
+  const long long base = ((long long)blockIdx.x * n_q_heads + head) * n_splits;
   pdl_wait();
   pdl_trigger();
-  const int head = blockIdx.y;
-  const int tok = cu_q[single_seqs[blockIdx.x]];
-  const long long base = ((long long)blockIdx.x * n_q_heads + head) * n_splits;
-  float mm = -INFINITY;
-  for (int z = 0; z < n_splits; ++z) mm = fmaxf(mm, part_ml[(base + z) * 2]);
-  for (int d = threadIdx.x; d < D; d += blockDim.x) {
-    float acc = 0.0f, lsum = 0.0f;
-    for (int z = 0; z < n_splits; ++z) {
-      const float mz = part_ml[(base + z) * 2];
-      if (mz == -INFINITY) continue;  // a split with no keys
-      const float f = exp2f(mz - mm);
-      acc += f * part_acc[(base + z) * D + d];
-      lsum += f * part_ml[(base + z) * 2 + 1];
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    float m[MERGE_MAX_SPLITS / 32], l[MERGE_MAX_SPLITS / 32];
+    float mm = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < MERGE_MAX_SPLITS / 32; ++i) {
+      const int z = lane + 32 * i;
+      const float2 ml = z < n_splits ? *reinterpret_cast<const float2*>(part_ml + (base + z) * 2)
+                                     : make_float2(-INFINITY, 0.0f);
+      m[i] = ml.x;
+      l[i] = ml.y;
+      mm = fmaxf(mm, ml.x);
     }
-    out[(long long)tok * out_stride + (long long)head * D + d] = from_f32<bf16>(acc / lsum);
+    mm = warp_max(mm);
+    float lsum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < MERGE_MAX_SPLITS / 32; ++i) {
+      const int z = lane + 32 * i;
+      const float f = m[i] == -INFINITY ? 0.0f : exp2f(m[i] - mm);   // a split with no keys weighs nothing
+      if (z < n_splits) weight[z] = f;
+      lsum += f * l[i];
+    }
+    // the sum over splits in a fixed order (a butterfly), whatever the batch
+    lsum = warp_sum(lsum);
+    if (lane == 0) inv_l = 1.0f / lsum;
+  }
+  __syncthreads();
+  for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    const float* col = part_acc + base * D + d;
+    float acc = 0.0f;
+    int z = 0;
+    for (; z + 8 <= n_splits; z += 8) {
+      float v[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[j] = weight[z + j] != 0.0f ? col[(long long)(z + j) * D] : 0.0f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc += weight[z + j] * v[j];
+    }
+    for (; z < n_splits; ++z) acc += weight[z] != 0.0f ? weight[z] * col[(long long)z * D] : 0.0f;
+    out[(long long)tok * out_stride + (long long)head * D + d] = from_f32<bf16>(acc * inv_l);
   }
 }
 
@@ -858,7 +892,7 @@ SI_API int si_attn_decode(const void* q, int q_stride, const void* pool, int n_p
   if (n_splits > 1 && !scratch) return SI_ERR_ARG;
   const int group = n_q_heads / n_kv_heads;
   const int grid_y = n_kv_heads * ((group + 15) / 16);
-  if (grid_y > 65535 || n_splits > 65535 || n_q_heads > 65535) return SI_ERR_TOO_LARGE;
+  if (grid_y > 65535 || n_splits > si::MERGE_MAX_SPLITS || n_q_heads > 65535) return SI_ERR_TOO_LARGE;
   if (n_single == 0) return SI_OK;
   SI_ALLOW_DYNAMIC_SMEM((si::attn_decode_kernel), (int)si::DECODE_SMEM);
   float* part_acc = scratch;

@@ -35,10 +35,46 @@ __global__ void embed_gather_kernel(const T* __restrict__ table, const int* __re
 //   x = residual[src] (+ delta[src]);  if (!rows && delta) residual[src] = x;
 //   out[r] = x * rsqrt(sum(x^2)/H + eps) * w
 // The row is kept in shared memory between the two passes.
+// The pending addend of a row comes either as one row of `delta` (dtype TA) or as `n_parts`
+// float32 slices `parts[p][row]` (partial sums of a product whose k-range was cut across
+// blocks): the slices are added in order and the sum rounded to TA, which is what the product
+// would have stored had it not been cut.
+struct DeltaParts {
+  const float* parts;
+  int n_parts;
+  long long stride;  // elements between slices
+};
+
+constexpr int MAX_DELTA_PARTS = 8;
+
+template <typename TA>
+__device__ __forceinline__ void sum_parts8(const DeltaParts& dp, size_t at, float (&d)[8]) {
+  // all slices are requested before the first is added (one round trip, not one per slice)
+  float v[MAX_DELTA_PARTS][8];
+#pragma unroll
+  for (int p = 0; p < MAX_DELTA_PARTS; ++p) {
+    if (p < dp.n_parts) {
+      load8<float>(dp.parts + (size_t)p * dp.stride + at, v[p]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[p][j] = 0.0f;
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) d[j] = v[0][j];
+#pragma unroll
+  for (int p = 1; p < MAX_DELTA_PARTS; ++p)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) d[j] += v[p][j];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) d[j] = to_f32<TA>(from_f32<TA>(d[j]));
+}
+
 template <typename TA, typename TW, bool VEC>
 __global__ void rmsnorm_kernel(float* __restrict__ residual, const TA* __restrict__ delta,
-                               const TW* __restrict__ weight, const int* __restrict__ rows,
-                               TA* __restrict__ out, int hidden, float eps) {
+                               DeltaParts dp, const TW* __restrict__ weight,
+                               const int* __restrict__ rows, TA* __restrict__ out, int hidden,
+                               float eps) {
   extern __shared__ float srow[];
   __shared__ float red[32];
   pdl_wait();
@@ -47,16 +83,18 @@ __global__ void rmsnorm_kernel(float* __restrict__ residual, const TA* __restric
   const int src = rows ? rows[r] : r;
   float* res = residual + (size_t)src * hidden;
   const TA* del = delta ? delta + (size_t)src * hidden : nullptr;
-  const bool write_back = (rows == nullptr) && (delta != nullptr);
+  const bool adds = delta != nullptr || dp.n_parts > 0;
+  const bool write_back = (rows == nullptr) && adds;
   TA* dst = out + (size_t)r * hidden;
   float ss = 0.0f;
   if (VEC) {  // hidden is a multiple of 8: 8 elements per thread and step
     for (int i = threadIdx.x * 8; i < hidden; i += blockDim.x * 8) {
       float x[8];
       load8<float>(res + i, x);
-      if (del) {
+      if (adds) {
         float d[8];
-        load8<TA>(del + i, d);
+        if (del) load8<TA>(del + i, d);
+        else sum_parts8<TA>(dp, (size_t)src * hidden + i, d);
 #pragma unroll
         for (int j = 0; j < 8; ++j) x[j] += d[j];
         if (write_back) store8<float>(res + i, x);
@@ -68,8 +106,14 @@ __global__ void rmsnorm_kernel(float* __restrict__ residual, const TA* __restric
   } else {
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
       float x = res[i];
-      if (del) {
-        x += to_f32<TA>(del[i]);
+      if (adds) {
+        if (del) {
+          x += to_f32<TA>(del[i]);
+        } else {
+          float d = 0.0f;
+          for (int p = 0; p < dp.n_parts; ++p) d += dp.parts[(size_t)p * dp.stride + (size_t)src * hidden + i];
+          x += to_f32<TA>(from_f32<TA>(d));
+        }
         if (write_back) res[i] = x;
       }
       srow[i] = x;
@@ -98,8 +142,9 @@ __global__ void rmsnorm_kernel(float* __restrict__ residual, const TA* __restric
 // before the sum is known, so a block has one round trip to memory instead of two.
 template <typename TA, typename TW>
 __global__ void rmsnorm_row_in_registers_kernel(float* __restrict__ residual, const TA* __restrict__ delta,
-                                                const TW* __restrict__ weight, const int* __restrict__ rows,
-                                                TA* __restrict__ out, int hidden, float eps) {
+                                                DeltaParts dp, const TW* __restrict__ weight,
+                                                const int* __restrict__ rows, TA* __restrict__ out,
+                                                int hidden, float eps) {
   __shared__ float red[32];
   const int i = threadIdx.x * 8;
   const bool mine = i < hidden;
@@ -114,9 +159,10 @@ __global__ void rmsnorm_row_in_registers_kernel(float* __restrict__ residual, co
   float ss = 0.0f;
   if (mine) {
     load8<float>(res + i, x);
-    if (delta) {
+    if (delta || dp.n_parts > 0) {
       float d[8];
-      load8<TA>(delta + (size_t)src * hidden + i, d);
+      if (delta) load8<TA>(delta + (size_t)src * hidden + i, d);
+      else sum_parts8<TA>(dp, (size_t)src * hidden + i, d);
 #pragma unroll
       for (int j = 0; j < 8; ++j) x[j] += d[j];
       if (rows == nullptr) store8<float>(res + i, x);
@@ -180,12 +226,14 @@ SI_API int si_embed_gather(const void* table, int table_dtype, const int* ids, f
 }
 
 template <typename TA, typename TW>
-static int launch_rmsnorm(float* residual, const void* delta, const void* weight, const int* rows,
-                          void* out, int n_rows, int hidden, float eps, cudaStream_t stream) {
+static int launch_rmsnorm(float* residual, const void* delta, si::DeltaParts dp, const void* weight,
+                          const int* rows, void* out, int n_rows, int hidden, float eps,
+                          cudaStream_t stream) {
   const size_t smem = (size_t)hidden * sizeof(float);
   if (smem > 200 * 1024) return SI_ERR_TOO_LARGE;
   const bool vec = hidden % 8 == 0 &&
-                   ((((uintptr_t)residual | (uintptr_t)delta | (uintptr_t)weight | (uintptr_t)out) & 15) == 0);
+                   ((((uintptr_t)residual | (uintptr_t)delta | (uintptr_t)weight | (uintptr_t)out |
+                      (uintptr_t)dp.parts) & 15) == 0) && dp.stride % 4 == 0;
   auto kern = vec ? si::rmsnorm_kernel<TA, TW, true> : si::rmsnorm_kernel<TA, TW, false>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -197,28 +245,38 @@ static int launch_rmsnorm(float* residual, const void* delta, const void* weight
   if (threads < 64) threads = 64;
   if (vec && hidden <= threads * 8) {
     SI_LAUNCH((si::rmsnorm_row_in_registers_kernel<TA, TW>), n_rows, threads, 0, stream, residual,
-              (const TA*)delta, (const TW*)weight, rows, (TA*)out, hidden, eps);
+              (const TA*)delta, dp, (const TW*)weight, rows, (TA*)out, hidden, eps);
     return SI_OK;
   }
-  SI_LAUNCH(kern, n_rows, threads, smem, stream, residual, (const TA*)delta, (const TW*)weight,
+  SI_LAUNCH(kern, n_rows, threads, smem, stream, residual, (const TA*)delta, dp, (const TW*)weight,
             rows, (TA*)out, hidden, eps);
   return SI_OK;
 }
 
 // act_dtype: dtype of delta and out.  weight_dtype: dtype of the gain.
-SI_API int si_rmsnorm(float* residual, const void* delta, const void* weight, const int* rows,
+// The addend is `delta` (one row per residual row) or, when delta is null and n_parts > 0,
+// the sum of the float32 slices parts[p] (p < n_parts, part_stride elements apart, each laid
+// out like delta), added in order and rounded to act_dtype.
+SI_API int si_rmsnorm(float* residual, const void* delta, const float* parts, int n_parts,
+                      long long part_stride, const void* weight, const int* rows,
                       void* out, int n_rows, int hidden, float eps, int act_dtype,
                       int weight_dtype, cudaStream_t stream) {
   if (!residual || !weight || !out || n_rows < 0 || hidden <= 0 || !(eps > 0.0f)) return SI_ERR_ARG;
+  if (n_parts < 0 || (n_parts > 0 && (!parts || delta || part_stride < 0))) return SI_ERR_ARG;
+  if (n_parts > si::MAX_DELTA_PARTS) return SI_ERR_TOO_LARGE;
   if (n_rows == 0) return SI_OK;
+  si::DeltaParts dp;
+  dp.parts = n_parts > 0 ? parts : nullptr;
+  dp.n_parts = n_parts;
+  dp.stride = part_stride;
   if (act_dtype == SI_F32 && weight_dtype == SI_F32)
-    return launch_rmsnorm<float, float>(residual, delta, weight, rows, out, n_rows, hidden, eps, stream);
+    return launch_rmsnorm<float, float>(residual, delta, dp, weight, rows, out, n_rows, hidden, eps, stream);
   if (act_dtype == SI_BF16 && weight_dtype == SI_F32)
-    return launch_rmsnorm<__nv_bfloat16, float>(residual, delta, weight, rows, out, n_rows, hidden, eps, stream);
+    return launch_rmsnorm<__nv_bfloat16, float>(residual, delta, dp, weight, rows, out, n_rows, hidden, eps, stream);
   if (act_dtype == SI_BF16 && weight_dtype == SI_BF16)
-    return launch_rmsnorm<__nv_bfloat16, __nv_bfloat16>(residual, delta, weight, rows, out, n_rows, hidden, eps, stream);
+    return launch_rmsnorm<__nv_bfloat16, __nv_bfloat16>(residual, delta, dp, weight, rows, out, n_rows, hidden, eps, stream);
   if (act_dtype == SI_F32 && weight_dtype == SI_BF16)
-    return launch_rmsnorm<float, __nv_bfloat16>(residual, delta, weight, rows, out, n_rows, hidden, eps, stream);
+    return launch_rmsnorm<float, __nv_bfloat16>(residual, delta, dp, weight, rows, out, n_rows, hidden, eps, stream);
   return SI_ERR_DTYPE;
 }
 

@@ -106,6 +106,10 @@ class StepContext:
     kv_lens: list[int] = field(default_factory=list)
     plans: dict[str, Any] = field(default_factory=dict)  # what each step planner returned
     fixed_shape: bool = False  # True inside a captured decode graph (sizes are capacities)
+    # set by the model and the blocks as the step runs: whether the norm that will add the
+    # output of the sub-layer now running takes ops.PartialSums (parts/base.py, Norm)
+    partial_sums_ok: bool = False
+    next_takes_partial_sums: bool = False
 
 
 _FEW_ROWS = 8            # up to this many changed block-table rows are copied span by span,

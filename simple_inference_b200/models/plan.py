@@ -168,7 +168,13 @@ class DecoderModel:
         """
         residual = self.embedding.forward(ctx.token_ids, ctx)
         delta = None
-        for step in self.plan.run_order:
+        order = self.plan.run_order
+        for i, step in enumerate(order):
+            # who adds this block's output to the residual stream: the next block's first norm,
+            # or the final norm
+            taker = self.blocks[order[i + 1].layer].first_norm() if i + 1 < len(order) \
+                else self.final_norm
+            ctx.next_takes_partial_sums = bool(taker is not None and taker.takes_partial_sums)
             cache = caches[step.cache_entry]
             if cache is not None and cache.writes != step.writes_cache:
                 cache = LayerCache(cache.spec, cache.group, cache.pool, cache.state,

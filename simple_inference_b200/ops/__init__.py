@@ -133,25 +133,54 @@ def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> t
     return out
 
 
+class PartialSums:
+    """The output of a product whose k-range was cut across blocks: float32 slices
+    ``[splits, rows, width]`` that whoever consumes them adds up, in order, and rounds to
+    ``dtype`` (what the product would have stored had it not been cut).  ``rmsnorm`` takes one
+    in place of ``delta``; ``tensor()`` is the sum for everyone else."""
+
+    def __init__(self, slices: torch.Tensor, dtype: torch.dtype):
+        self.slices = slices
+        self.dtype = dtype
+        self.shape = tuple(slices.shape[1:])
+
+    def tensor(self) -> torch.Tensor:
+        total = self.slices[0].clone()
+        for p in range(1, self.slices.shape[0]):
+            total += self.slices[p]
+        return total.to(self.dtype)
+
+
 def rmsnorm(residual: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor,
-            delta: torch.Tensor | None = None, rows: torch.Tensor | None = None) -> torch.Tensor:
+            delta: "torch.Tensor | PartialSums | None" = None,
+            rows: torch.Tensor | None = None) -> torch.Tensor:
     """RMSNorm of rows of the float32 residual, with the pending add fused in.
 
     Without ``rows``: ``residual += delta`` (if given) in place, ``out = norm(residual)``.
     With ``rows``: ``out[r] = norm(residual[rows[r]] + delta[rows[r]])``, residual untouched.
+    ``delta`` may be the ``PartialSums`` of a product.
     """
-    _dev(residual, weight, out, delta, rows)
+    parts = None
+    if isinstance(delta, PartialSums):
+        parts, delta = delta.slices, None
+    _dev(residual, weight, out, delta, rows, parts)
     _i32(rows, "rows")
     n_rows, hidden = out.shape
     if residual.dtype != torch.float32 or residual.shape[1] != hidden or weight.numel() != hidden:
         raise KernelError("rmsnorm: shape or dtype mismatch")
     if delta is not None and (delta.dtype != out.dtype or delta.shape[1] != hidden):
         raise KernelError("rmsnorm: delta must have the dtype of out and the width of residual")
+    if parts is not None and (parts.dtype != torch.float32 or parts.dim() != 3 or
+                              parts.shape[2] != hidden):
+        raise KernelError("rmsnorm: partial sums must be float32 [splits, rows, width of residual]")
     if rows is None and residual.shape[0] < n_rows:
         raise KernelError("rmsnorm: fewer residual rows than output rows")
     if rows is not None and rows.numel() < n_rows:
         raise KernelError("rmsnorm: fewer row indices than output rows")
-    _check(core().si_rmsnorm(_p(residual), _p(delta), _p(weight), _p(rows), _p(out), n_rows,
+    _check(core().si_rmsnorm(_p(residual), _p(delta), _p(parts),
+                             0 if parts is None else parts.shape[0],
+                             ctypes.c_longlong(0 if parts is None else parts.stride(0)),
+                             _p(weight), _p(rows), _p(out), n_rows,
                              hidden, _c_float(eps), _dt(out), _dt(weight), _stream()), "rmsnorm")
     return out
 
@@ -259,6 +288,36 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> torch.Te
     else:
         torch.mm(x, weight.t(), out_dtype=torch.float32, out=out)
     return out
+
+
+def linear_for_residual(x: torch.Tensor, weight: torch.Tensor, ws, tag: str,
+                        partial_ok: bool) -> "torch.Tensor | PartialSums":
+    """``x @ weight.T`` for a product whose output is only ever added to the residual stream.
+
+    With few rows and a consumer that takes them (``partial_ok``), the weight-streaming kernel
+    cuts the k-range across blocks so that a narrow matrix still keeps every SM fetching, and
+    returns ``PartialSums``; otherwise an ordinary tensor in ``x``'s dtype.  ``ws`` is the
+    step's workspace, ``tag`` names the buffers.
+    """
+    m, k = x.shape
+    n = weight.shape[0]
+    if partial_ok and _skinny_ok(x, weight):
+        splits = core().si_gemm_skinny_splits(n, k)
+        if splits > 1:
+            _dev(x, weight)
+            if weight.shape[1] != k or x.dtype != weight.dtype:
+                raise KernelError("linear_for_residual: shapes or dtypes do not fit")
+            slices = ws.get(tag + ".parts", (SKINNY_MAX_SPLITS * SKINNY_MAX_ROWS, n), torch.float32,
+                            row_cap=SKINNY_MAX_SPLITS * SKINNY_MAX_ROWS)
+            slices = slices[:splits * m].view(splits, m, n)
+            _check(core().si_gemm_skinny_bf16(_p(x), x.stride(0), _p(weight), _p(slices), n,
+                                              m, n, k, 4, _stream()), "gemm_skinny_partial")
+            return PartialSums(slices, x.dtype)
+    out = ws.get(tag, (m, n), x.dtype)
+    return linear(x, weight, out)
+
+
+SKINNY_MAX_SPLITS = 8   # most k-ranges the weight-streaming product cuts a matrix into
 
 
 def can_fuse_swiglu(x: torch.Tensor, weight: torch.Tensor) -> bool:
@@ -510,5 +569,6 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
 
 
 __all__ = ["KernelError", "KernelBuildError", "embed_gather", "rmsnorm", "swiglu", "linear", "linear_swiglu", "linear_tc",
+           "linear_for_residual", "PartialSums",
            "can_fuse_swiglu", "check_status", "status_tensor",
            "rope_kv_store", "can_fuse_projection_rope", "linear_rope_kv_store", "attention_generic", "paged_attention", "attention_prefill_wide", "wide_prefill_fits", "plan_kv_splits", "sample", "core", "attention_library"]

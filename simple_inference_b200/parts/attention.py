@@ -77,6 +77,5 @@ class PagedAttention(Mixer):
         ops.paged_attention(qkv, cache.pool, ctx, ctx.plans.get(PagedAttentionPlanner.name),
                             cache.group, mixed, self.num_heads,
                             self.num_kv_heads, self.head_dim, self.scale, self.window)
-        out = ctx.ws.get("attn.proj", (n, self.hidden_size), x.dtype)
-        ops.linear(mixed, self.w_o, out)
-        return out
+        return ops.linear_for_residual(mixed, self.w_o, ctx.ws, "attn.proj",
+                                       getattr(ctx, "partial_sums_ok", False))

@@ -177,7 +177,13 @@ class Norm(Part):
     adds ``delta`` (a sub-layer's output not yet added) into ``residual`` in
     place, in 32-bit, then normalises; ``rows`` restricts both to some rows and
     leaves ``residual`` untouched (used before the output head).
+
+    A norm whose ``takes_partial_sums`` is True accepts an ``ops.PartialSums`` as ``delta``
+    (the float32 slices of a product cut along k, which it adds up itself); the sub-layer
+    before it may then hand its output over in that form (``ctx.partial_sums_ok``).
     """
+
+    takes_partial_sums = False
 
     def forward(self, residual: torch.Tensor, ctx: "StepContext", tag: str = "norm") -> torch.Tensor:
         raise NotImplementedError
@@ -270,6 +276,11 @@ class Block(Part):
     def forward(self, residual: torch.Tensor, delta: torch.Tensor | None,
                 ctx: "StepContext", cache: LayerCache | None) -> torch.Tensor:
         raise NotImplementedError
+
+    def first_norm(self) -> "Norm | None":
+        """The norm that takes the previous block's pending output (``delta``), if the block
+        can tell: the model uses it to learn whether that output may come as partial sums."""
+        return None
 
     def step_planners(self) -> list[type[StepPlanner]]:
         return self.mixer.step_planners()

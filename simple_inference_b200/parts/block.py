@@ -40,8 +40,19 @@ class PreNormBlock(Block):
             own = {k[len(prefix) + 1:]: v for k, v in tensors.items() if k.startswith(prefix + ".")}
             part.bind(own, rt)
 
+    def first_norm(self):
+        return self.mixer_norm
+
     def forward(self, residual, delta, ctx, cache: LayerCache | None):
+        # ctx.partial_sums_ok tells a sub-layer whether the norm that will add its output takes
+        # partial sums: for the mixer that is this block's second norm, for the feed-forward
+        # whatever follows the block (the model said so in ctx.next_takes_partial_sums)
+        after_block = getattr(ctx, "next_takes_partial_sums", False)
         h = self.mixer_norm.add_forward(residual, delta, ctx)
+        ctx.partial_sums_ok = self.feed_forward_norm.takes_partial_sums
         mixed = self.mixer.forward(h, ctx, cache)
         h = self.feed_forward_norm.add_forward(residual, mixed, ctx)
-        return self.feed_forward.forward(h, ctx)
+        ctx.partial_sums_ok = after_block
+        out = self.feed_forward.forward(h, ctx)
+        ctx.partial_sums_ok = False
+        return out

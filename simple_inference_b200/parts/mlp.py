@@ -46,6 +46,5 @@ class SwiGLU(FeedForward):
             gate_up = ctx.ws.get("mlp.gate_up", (n, 2 * self.intermediate_size), x.dtype)
             ops.linear(x, self.w_gate_up, gate_up)
             ops.swiglu(gate_up, hidden)
-        out = ctx.ws.get("mlp.down", (n, self.hidden_size), x.dtype)
-        ops.linear(hidden, self.w_down, out)
-        return out
+        return ops.linear_for_residual(hidden, self.w_down, ctx.ws, "mlp.down",
+                                       getattr(ctx, "partial_sums_ok", False))

@@ -20,6 +20,8 @@ from .registry import register_norm
 
 @register_norm("rmsnorm")
 class RMSNorm(Norm):
+    takes_partial_sums = True   # the kernel adds up the slices of a product cut along k
+
     def __init__(self, hidden_size: int, eps: float):
         self.hidden_size = int(hidden_size)
         self.eps = float(eps)

@@ -460,6 +460,50 @@ def test_weight_streaming_product_for_few_rows(ops, m, n, k):
     assert torch.equal(one[0], out32[m - 1])
 
 
+@pytest.mark.parametrize("m,n,k", [(8, 3072, 3072), (3, 400, 2048), (16, 3072, 8192), (5, 50, 64),
+                                   (1, 1000, 1024), (9, 200, 5000)])
+def test_product_cut_along_k_and_the_norm_that_adds_its_slices(ops, m, n, k):
+    """Products that feed the residual stream may leave their sum to the RMSNorm that follows:
+    float32 slices, one per k-range, added in a fixed order.  The norm given the slices must do
+    exactly what it does given the rounded sum."""
+    from simple_inference_b200.engine.batch import Workspace
+    g = gen(11)
+    x = (torch.randn(m, k, device=dev(), generator=g) * 0.5).bfloat16()
+    w = (torch.randn(n, k, device=dev(), generator=g) * 0.1).bfloat16()
+    ref = x.float() @ w.float().T
+    ws = Workspace(dev(), 64)
+    parts = ops.linear_for_residual(x, w, ws, "t", True)
+    splits = ops.core().si_gemm_skinny_splits(n, k)
+    assert splits == (1 if k < 1024 else splits) and 1 <= splits <= ops.SKINNY_MAX_SPLITS
+    assert splits > 1 or (n, k) == (50, 64), "the larger cases here are all cut"
+    if splits == 1:
+        assert isinstance(parts, torch.Tensor) and parts.dtype == torch.bfloat16
+        assert (parts.float() - ref).abs().max() < 8e-3 * max(1.0, float(ref.abs().max()))
+        return
+    assert isinstance(parts, ops.PartialSums) and parts.slices.shape == (splits, m, n)
+    assert (parts.slices.sum(0) - ref).abs().max() < 1e-4 * max(1.0, float(ref.abs().max()))
+    whole = parts.tensor()
+    assert whole.dtype == torch.bfloat16
+    plain = ops.linear_for_residual(x, w, ws, "u", False)          # the same product, not cut
+    assert isinstance(plain, torch.Tensor)
+    assert (whole.float() - plain.float()).abs().max() <= 2 ** -7 * float(plain.float().abs().max())
+    gain = 1 + 0.1 * torch.randn(n, device=dev(), generator=g)
+    res = torch.randn(m, n, device=dev(), generator=g)
+    r1, r2 = res.clone(), res.clone()
+    o1 = torch.empty(m, n, device=dev(), dtype=torch.bfloat16)
+    o2 = torch.empty_like(o1)
+    ops.rmsnorm(r1, gain, 1e-5, o1, delta=parts)
+    ops.rmsnorm(r2, gain, 1e-5, o2, delta=whole)
+    assert torch.equal(r1, r2) and torch.equal(o1, o2)
+    rows = torch.tensor([m - 1, 0], device=dev(), dtype=torch.int32)
+    o3 = torch.empty(2, n, device=dev(), dtype=torch.bfloat16)
+    o4 = torch.empty_like(o3)
+    r3 = res.clone()
+    ops.rmsnorm(r3, gain, 1e-5, o3, delta=parts, rows=rows)
+    ops.rmsnorm(res.clone(), gain, 1e-5, o4, delta=whole, rows=rows)
+    assert torch.equal(o3, o4) and torch.equal(r3, res)
+
+
 @pytest.mark.parametrize("m,n,k", [(256, 512, 64), (300, 264, 72), (257, 40, 8), (2048, 3072, 3072),
                                    (700, 5120, 200)])
 def test_tensor_memory_product_on_sm_pairs(ops, m, n, k):
