@@ -233,6 +233,135 @@ def time_prefill(model, cfg, reps=5):
     return sorted(times[2:])[len(times[2:]) // 2]
 
 
+LLAMA_3_2_1B = dict(LLAMA_3_2_3B, num_hidden_layers=16, hidden_size=2048, num_attention_heads=32,
+                    num_key_value_heads=8, head_dim=64, intermediate_size=8192)
+LLAMA_3_1_8B = dict(LLAMA_3_2_3B, num_hidden_layers=32, hidden_size=4096, num_attention_heads=32,
+                    num_key_value_heads=8, head_dim=128, intermediate_size=14336,
+                    tie_word_embeddings=False,
+                    rope_scaling=dict(LLAMA_3_2_3B["rope_scaling"], factor=8.0))
+
+
+def workload_1b_continuous_batching(pk):
+    """The reference's continuous-batching workload at the Llama 3.2 1B shape: 64 requests, prompt
+    lengths uniform in 128..2048 (seeded), 256 output tokens each, all queued at once and run
+    through ``InferenceEngine.step()`` until done (random weights, greedy, no stop token)."""
+    import torch
+    from simple_inference_b200 import InferenceEngine
+    from simple_inference_b200.engine import RequestState
+    from simple_inference_b200.models.load import random_model
+    cfg, model = random_model(dict(LLAMA_3_2_1B), seed=1, dtype="bfloat16", device="cuda:0")
+    n_req, n_out = 64, 256
+    g = torch.Generator().manual_seed(11)
+    lens = torch.randint(128, 2049, (n_req,), generator=g).tolist()
+    prompts = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in lens]
+    eng = InferenceEngine(model, max_running=n_req, max_seq_len=2048 + n_out, block_size=PAGE_SIZE,
+                          eos_id=-1, temperature=0.0, max_tokens_per_step=2048, warmup=True)
+    reqs = [eng.add_request(p, n_out) for p in prompts]
+    layer_params, head_params = matmul_params(cfg)
+    weight_bytes = 2 * (layer_params + head_params)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    steps = decode_steps = 0
+    decode_s = decode_bytes = 0.0
+    while eng.has_work():
+        running = eng.scheduler.running
+        all_decoding = (not eng.scheduler.waiting and len(running) == n_req and
+                        all(r.state is RequestState.DECODE for r in running))
+        live = sum(r.pos + 1 for r in running) if all_decoding else 0
+        t1 = time.perf_counter()
+        eng.step()
+        if all_decoding:   # a step of 64 decoded tokens and nothing else (the sampled ids came home)
+            decode_s += time.perf_counter() - t1
+            decode_bytes += weight_bytes + live * kv_bytes_per_token(cfg)
+            decode_steps += 1
+        steps += 1
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    assert all(len(r.generated) == n_out for r in reqs)
+    out = {
+        "model": "llama-3.2-1b-shape", "layers": cfg.num_hidden_layers, "hidden": cfg.hidden_size,
+        "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
+        "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
+        "requests": n_req, "prompt_tokens": sum(lens), "output_tokens": n_req * n_out,
+        "wall_s": round(wall, 3), "engine_steps": steps,
+        "output_tok_s": round(n_req * n_out / wall, 1),
+        "total_tok_s": round((sum(lens) + n_req * n_out) / wall, 1),
+    }
+    if decode_steps:
+        achieved = decode_bytes / decode_s / 1e9
+        out["decode_b64"] = {"steps": decode_steps, "ms_per_step": round(decode_s / decode_steps * 1e3, 4),
+                             "tok_s": round(n_req * decode_steps / decode_s, 1),
+                             "roofline_frac": round(achieved / pk["hbm_gbs"], 4), "gb_s": round(achieved, 1)}
+    eng.reset()
+    del eng, model
+    torch.cuda.empty_cache()
+    return out
+
+
+def workload_8b_long_context(pk):
+    """The long-context workload at the Llama 3.1 8B shape: 16 prompts of 8,192 ids run in portions
+    of 2,048 tokens, then decoding at batch 16 over 17 GB of cache, through ``InferenceEngine.step()``."""
+    import torch
+    from simple_inference_b200 import InferenceEngine
+    from simple_inference_b200.engine import RequestState
+    from simple_inference_b200.models.load import random_model
+    cfg, model = random_model(dict(LLAMA_3_1_8B), seed=2, dtype="bfloat16", device="cuda:0")
+    n_req, n_prompt, n_out = 16, 8192, 48
+    g = torch.Generator().manual_seed(12)
+    prompts = [torch.randint(0, cfg.vocab_size, (n_prompt,), generator=g).tolist() for _ in range(n_req)]
+    eng = InferenceEngine(model, max_running=n_req, max_seq_len=n_prompt + 2 * n_out + n_req * 4,
+                          block_size=PAGE_SIZE, eos_id=-1, temperature=0.0, max_tokens_per_step=2048 + n_req,
+                          chunk_size=2048, warmup=True)
+    for p in prompts:   # earlier requests decode while later ones are still being read
+        eng.add_request(p, n_out + 4 * n_req)
+    layer_params, head_params = matmul_params(cfg)
+    weight_bytes = 2 * (layer_params + head_params)   # untied: the head is streamed, embedding rows are gathered
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    prefill_steps = 0
+    while eng.scheduler.waiting or any(r.state is RequestState.PREFILL for r in eng.scheduler.running) \
+            or not eng.scheduler.running:
+        eng.step()
+        prefill_steps += 1
+    torch.cuda.synchronize()
+    prefill_s = time.perf_counter() - t0
+    T, d = n_prompt, cfg.head_dim
+    flops_per_prompt = 2 * T * layer_params + 2 * head_params \
+        + cfg.num_hidden_layers * 2 * cfg.num_attention_heads * d * T * (T + 1)
+    for _ in range(3):
+        eng.step()
+    torch.cuda.synchronize()
+    steps, live_sum = 20, 0
+    t1 = time.perf_counter()
+    for _ in range(steps):
+        live_sum += sum(r.pos + 1 for r in eng.scheduler.running)
+        assert len(eng.step()) == n_req
+    torch.cuda.synchronize()
+    decode_s = time.perf_counter() - t1
+    step_bytes = weight_bytes + live_sum / steps * kv_bytes_per_token(cfg)
+    achieved = step_bytes / (decode_s / steps) / 1e9
+    out = {
+        "model": "llama-3.1-8b-shape", "layers": cfg.num_hidden_layers, "hidden": cfg.hidden_size,
+        "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
+        "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
+        "tied": False, "requests": n_req, "prompt_tokens_each": n_prompt, "portion": 2048,
+        "prefill": {"tok_s": round(n_req * n_prompt / prefill_s, 1), "s": round(prefill_s, 3),
+                    "engine_steps": prefill_steps,
+                    "frac_of_sustained_peak": round(n_req * flops_per_prompt / prefill_s /
+                                                    (pk["bf16_tflops_sustained"] * 1e12), 4),
+                    "note": "earlier requests decode beside the later prompts' portions"},
+        "decode_b16": {"tok_s": round(n_req * steps / decode_s, 1),
+                       "ms_per_step": round(decode_s / steps * 1e3, 4),
+                       "mean_context": round(live_sum / steps / n_req, 1),
+                       "gb_per_step": round(step_bytes / 1e9, 2), "gb_s": round(achieved, 1),
+                       "roofline_frac": round(achieved / pk["hbm_gbs"], 4)},
+    }
+    eng.reset()
+    del eng, model
+    torch.cuda.empty_cache()
+    return out
+
+
 def run_reference(args) -> int:
     """Run ``baseline/reference_arm.py`` in a process of its own (so that nothing of this
     package is imported beside the reference) and pass its JSON line on."""
@@ -268,6 +397,8 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=None, help="run fewer layers (named in config)")
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
+    ap.add_argument("--no-workloads", action="store_true",
+                    help="skip the 1B continuous-batching and 8B long-context workloads")
     ap.add_argument("--only", choices=["decode", "prefill"],
                     help="run one part and print a short record (for profiling; not the contract line)")
     ap.add_argument("--eager", action="store_true", help="no CUDA graphs (for kernel-level profiles)")
@@ -341,6 +472,18 @@ def main() -> int:
             points[f"decode_b{b}"] = round(b / (pms * 1e-3), 1)
             graph_check[f"b{b}"] = check
 
+    workloads = {}
+    if not args.no_workloads:
+        del model
+        torch.cuda.empty_cache()
+        for name, fn in (("llama_1b_continuous_batching", workload_1b_continuous_batching),
+                         ("llama_8b_long_context", workload_8b_long_context)):
+            try:
+                workloads[name] = fn(pk)
+            except Exception as e:   # the headline stands without them; say what went wrong
+                workloads[name] = {"error": f"{type(e).__name__}: {e}"[:300]}
+                torch.cuda.empty_cache()
+
     line = {
         "metric": "decode tok/s, Llama 3.2 3B shape, batch 8, context 2048 (1 GPU)",
         "value": round(args.batch / (ms * 1e-3), 1), "unit": "tokens/s", "n_gpus": 1,
@@ -368,6 +511,7 @@ def main() -> int:
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"],
                      "unit": "GB/s", "frac": round(achieved / pk["hbm_gbs"], 4)},
         "points": points,
+        "workloads": workloads,
         "graph_check": graph_check,
         "clocks": clocks,
     }

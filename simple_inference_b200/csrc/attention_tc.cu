@@ -116,12 +116,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
     }
     mbar_init_fence();
   }
-  if (warp == 1) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                 ::"r"(tmem_slot), "r"(512u) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-    tmem_fence_before();
-  }
   // ---- this block's tile (the step's batch description was on the device before its first
   // kernel: read it before waiting for the kernel that wrote Q, K and V)
   const int tile_id = blockIdx.y;  // the host lists the longest tiles first; heads vary fastest
@@ -152,13 +146,22 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
     }
   }
   fence_proxy_async_smem();
+  // Tensor memory is taken only after the wait on the preceding kernel: a block that is resident
+  // while an earlier kernel still runs must not hold its SM's 512 columns through that wait (a
+  // block of the earlier kernel that has yet to allocate there would never get them).
+  pdl_wait();
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(tmem_slot), "r"(512u) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    tmem_fence_before();
+  }
   __syncthreads();
   tmem_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
   // The softmax warps hold a row of S (128 values) and the P they make of it: the first
   // warpgroup (producers and issuers) hands them the registers it does not need.
   // (the two instructions stand at the head of the two branches below)
-  pdl_wait();
 
   // Tensor memory: S of tile t in columns [128 b, 128 b + 128) with b = t & 1; P of tile t,
   // bfloat16 pairs, over the first 64 columns of the same buffer once S has been read;

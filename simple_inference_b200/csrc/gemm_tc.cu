@@ -90,6 +90,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     }
     mbar_init_fence();
   }
+  // The inputs must be complete, and only then is tensor memory taken: a block that is resident
+  // while the kernel before it still runs must not hold its SM's 512 columns through the wait
+  // (a block of an earlier kernel that has yet to allocate there would never get them).
+  pdl_wait();
   if (warp == 1) {  // the whole warp allocates tensor memory, and later frees it
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
                  ::"r"(tmem_slot), "r"(TC_TMEM_COLS) : "memory");
@@ -99,7 +103,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
   __syncthreads();
   tmem_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
-  pdl_wait();  // barriers and tensor memory are set up; now the inputs must be complete
 
   if (warp == 0) {
     if (lane == 0) {  // ---------------------------------------------- TMA producer

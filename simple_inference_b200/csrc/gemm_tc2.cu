@@ -132,6 +132,11 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     }
     mbar_init_fence();
   }
+  // Tensor memory is taken only AFTER the wait on the preceding kernel.  A block of this kernel
+  // may be resident while the kernel before it still runs; holding all 512 columns of its SM
+  // through that wait starves any block of an earlier kernel that has yet to allocate there
+  // (seen as a stall of whole steps with long prompt portions beside decoded tokens).
+  pdl_wait();
   if (warp == 1) {  // one warp of each block: the pair's tensor memory is allocated together
     asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
                  ::"r"(tmem_slot), "r"(T2_TMEM_COLS) : "memory");
@@ -142,7 +147,6 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
   cluster_sync();  // both blocks' barriers exist before either signals the other's
   tmem_fence_after();
   const uint32_t tmem_base = *tmem_slot_ptr;
-  pdl_wait();
 
   if (warp == 0) {
     if (lane == 0) {  // ---------------------------------------------- TMA producer
