@@ -119,12 +119,15 @@ __device__ __forceinline__ void tile_rows(int tile, int N, const RopeEpilogue& r
 // the n_tiles row tiles, one after the other, with its warps' rings running on across the
 // tiles.  k_per_block: a multiple of SK_WARPS * SK_STAGE_K.
 template <int NT, int EPI>
-__global__ void __launch_bounds__(SK_THREADS)
+__global__ void __launch_bounds__(SK_THREADS, SK_BLOCKS_PER_SM)
 skinny_gemm_kernel(const bf16* __restrict__ X, int ldx, const bf16* __restrict__ W,
                    void* __restrict__ out, int ldo, int M, int N, int K, int k_per_block,
                    int n_tiles, RopeEpilogue rope) {
   extern __shared__ __align__(128) unsigned char sk_smem[];
-  __shared__ float red[2][SK_WARPS][16][NT * 8 + 1];   // two, so that a tile costs one barrier
+  // two buffers for up to 8 tokens, so that a tile costs one barrier; one for 16 tokens, where
+  // a second would take the fourth block's place on the SM
+  constexpr int RED_BUFS = NT == 1 ? 2 : 1;
+  __shared__ float red[RED_BUFS][SK_WARPS][16][NT * 8 + 1];
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
@@ -240,7 +243,7 @@ skinny_gemm_kernel(const bf16* __restrict__ X, int ldx, const bf16* __restrict__
   // ---- the end of a tile: the four warps' sums meet in shared memory, then the epilogue
   int m_i = 0, m_tile = blockIdx.x, m_j = 0;   // stage in its tile, tile, and how many tiles are done
   auto finish_tile = [&]() {
-    float (*rd)[16][NT * 8 + 1] = red[m_j & 1];
+    float (*rd)[16][NT * 8 + 1] = red[m_j % RED_BUFS];
     // partial sums of this warp: rows g, g+8 of the tile, tokens 2t, 2t+1 of each n-tile
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) {
@@ -323,6 +326,7 @@ skinny_gemm_kernel(const bf16* __restrict__ X, int ldx, const bf16* __restrict__
         }
       }
     }
+    if (RED_BUFS == 1) __syncthreads();   // everyone has read the sums before the next tile's are written
     m_tile += gridDim.x;
     ++m_j;
   };
