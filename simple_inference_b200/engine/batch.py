@@ -167,6 +167,10 @@ class BatchBuilder:
         self._host_views: dict[str, np.ndarray] = {}
         self._device_views: dict[tuple, dict] = {}
         self._plan_dev = {name: self._d(f"plan:{name}") for name in self.planners}
+        self._plan_host = {name: self._h(f"plan:{name}") for name in self.planners}
+        self._front_dev, self._front_host = self.dev[:self.front], self.host[:self.front]
+        self._group_info = [(g, grp, grp.page_size, grp.window is None)
+                            for g, grp in enumerate(cache.groups)]
         self._host_tables = [self.host[self._off[f"block_table{g}"][0]:][:max_seqs * self.table_len[g]]
                              .view(max_seqs, self.table_len[g]) for g in range(self.n_groups)]
         self._dev_tables = [self._d(f"block_table{g}").view(max_seqs, self.table_len[g])
@@ -229,21 +233,20 @@ class BatchBuilder:
                 token_ids[t:t + n] = e.tokens
                 positions[t:t + n] = np.arange(start, end, dtype=np.int32)
                 tok_seq[t:t + n] = s
-            for g, grp in enumerate(cache.groups):
+            serial = cache.admission(e.request)
+            for g, grp, ps, keeps_all in self._group_info:
                 table = cache.block_table(e.request, g)
-                row = tables[g][s]
+                n_pages = len(table)
                 owner = self._row_owner[g][s]
-                serial = cache.admission(e.request)
-                if grp.window is None and owner is not None and owner[0] == serial \
-                        and owner[1] <= len(table):
-                    if owner[1] < len(table):
-                        row[owner[1]:len(table)] = table[owner[1]:]   # only the new pages
-                        dirty[g].append((s, owner[1], len(table)))
+                if keeps_all and owner is not None and owner[0] == serial and owner[1] <= n_pages:
+                    if owner[1] < n_pages:
+                        tables[g][s, owner[1]:n_pages] = table[owner[1]:]   # only the new pages
+                        dirty[g].append((s, owner[1], n_pages))
+                        self._row_owner[g][s] = (serial, n_pages)
                 else:
-                    row[:len(table)] = table
-                    dirty[g].append((s, 0, len(table)))
-                self._row_owner[g][s] = (serial, len(table))
-                ps = grp.page_size
+                    tables[g][s, :n_pages] = table
+                    dirty[g].append((s, 0, n_pages))
+                    self._row_owner[g][s] = (serial, n_pages)
                 if n == 1:
                     page = table[start // ps]
                     if page < 0:
@@ -278,10 +281,10 @@ class BatchBuilder:
             t += 1
             cu_q[s + 1] = t
         S += pad; N = t
-        plans = {name: planner.plan(self._h(f"plan:{name}"), self._plan_dev[name], q_lens, first)
+        plans = {name: planner.plan(self._plan_host[name], self._plan_dev[name], q_lens, first)
                  for name, planner in self.planners.items()}
 
-        self.dev[:self.front].copy_(self.host[:self.front], non_blocking=True)
+        self._front_dev.copy_(self._front_host, non_blocking=True)
         self.copied_words = self.front
         for g in range(self.n_groups):
             spans = dirty[g]

@@ -65,6 +65,9 @@ class PagedAttentionPlanner(StepPlanner):
         self._seg: dict[str, tuple[int, int]] = {}
         self._views: dict[tuple, dict] = {}
         self._dev: torch.Tensor | None = None
+        self._host: np.ndarray | None = None
+        self._h: dict[str, np.ndarray] = {}
+        self._all_single = -1   # how many leading entries of single_seqs hold 0, 1, 2, ... already
 
     def words(self, max_tokens: int, max_seqs: int) -> int:
         max_tiles = (max_tokens // QUERY_TILE + max_seqs + 2) // 2 * 2
@@ -78,7 +81,17 @@ class PagedAttentionPlanner(StepPlanner):
 
     def plan(self, host: np.ndarray, dev: torch.Tensor, q_lens: list[int],
              starts: list[int]) -> AttentionStepPlan:
-        h = {name: host[o:o + n] for name, (o, n) in self._seg.items()}
+        if self._host is not host:
+            self._host, self._all_single = host, -1
+            self._h = {name: host[o:o + n] for name, (o, n) in self._seg.items()}
+        h = self._h
+        if max(q_lens) == 1:   # decoding only: every sequence is single, and the list is 0, 1, 2, ...
+            n = len(q_lens)
+            if self._all_single < n:
+                h["single_seqs"][:n] = np.arange(n, dtype=np.int32)
+                self._all_single = n
+            return self._result(dev, n, 0, 0, 0, 1)
+        self._all_single = -1
         n_single = n_tiles = 0
         tile_work: list[int] = []
         wide: list[tuple[int, int, int]] = []  # (keys its last row sees, sequence, first row)
@@ -100,9 +113,13 @@ class PagedAttentionPlanner(StepPlanner):
             h["wide_seq"][i] = s
             h["wide_start"][i] = q0
 
+        return self._result(dev, n_single, n_tiles, n_pairs, len(wide), max(q_lens) if q_lens else 0)
+
+    def _result(self, dev: torch.Tensor, n_single: int, n_tiles: int, n_pairs: int, n_wide: int,
+                max_q_len: int) -> AttentionStepPlan:
         if self._dev is not dev:
             self._dev, self._views = dev, {}
-        sizes = (n_single, n_tiles, n_pairs, len(wide))
+        sizes = (n_single, n_tiles, n_pairs, n_wide)
         v = self._views.get(sizes)
         if v is None:  # views are made once per distinct set of sizes: slicing costs more than filling
             if len(self._views) >= 512:
@@ -114,9 +131,9 @@ class PagedAttentionPlanner(StepPlanner):
             v = self._views[sizes] = dict(
                 single_seqs=d("single_seqs", n_single), tile_seq=d("tile_seq", n_tiles),
                 tile_start=d("tile_start", n_tiles), tile_pairs=d("tile_pairs", 2 * n_pairs),
-                wide_seq=d("wide_seq", len(wide)), wide_start=d("wide_start", len(wide)))
+                wide_seq=d("wide_seq", n_wide), wide_start=d("wide_start", n_wide))
         return AttentionStepPlan(n_single=n_single, n_tiles=n_tiles, n_pairs=n_pairs,
-                                 n_wide=len(wide), max_q_len=max(q_lens) if q_lens else 0, **v)
+                                 n_wide=n_wide, max_q_len=max_q_len, **v)
 
 
 def plan_on_device(q_lens: list[int], starts: list[int], device: torch.device) -> AttentionStepPlan:
