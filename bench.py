@@ -153,6 +153,108 @@ def time_decode(model, cfg, batch, steps, warmup, sample_clocks=False):
     return ms, launches, ctx_mean, (clocks.summary() if clocks else None), check
 
 
+def time_products(cfg, batch):
+    """The matrix products of a decode step, each on its own: 28 copies of one layer's matrix (so
+    that every launch streams its weights from memory) run back to back from a CUDA graph, as
+    they follow each other in a step; microseconds per product and the rate at which it streams
+    its weights.  Kernels timed alone under a profiler cannot show what the prefetch before the
+    wait on the preceding kernel gains; this can."""
+    import torch
+    from simple_inference_b200 import ops
+    from simple_inference_b200.engine.batch import Workspace
+    dev = torch.device("cuda:0")
+    h, d = cfg.hidden_size, cfg.head_dim
+    qkv_rows = (cfg.num_attention_heads + 2 * cfg.num_key_value_heads) * d
+    shapes = [("qkv", qkv_rows, h, "plain"), ("o", h, cfg.num_attention_heads * d, "residual"),
+              ("gate_up", cfg.intermediate_size, h, "swiglu"), ("down", h, cfg.intermediate_size, "residual"),
+              ("head", cfg.vocab_size, h, "logits")]
+    ws = Workspace(dev, max(batch, 16))
+    out = {"batch": batch}
+    for name, n, k, kind in shapes:
+        rows = 2 * n if kind == "swiglu" else n
+        copies = 4 if kind == "logits" else cfg.num_hidden_layers
+        mats = [torch.randn(rows, k, device=dev).bfloat16() * 0.02 for _ in range(copies)]
+        x = torch.randn(batch, k, device=dev).bfloat16()
+        y = torch.empty(batch, n, device=dev, dtype=torch.float32 if kind == "logits" else torch.bfloat16)
+
+        def run(w):
+            if kind == "swiglu" and ops.can_fuse_swiglu(x, w):
+                ops.linear_swiglu(x, w, y)
+            elif kind == "residual":
+                ops.linear_for_residual(x, w, ws, "bench", True)
+            else:
+                ops.linear(x, w[:n], y)
+        for w in mats:
+            run(w)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(3):
+                for w in mats:
+                    run(w)
+        g.replay()
+        torch.cuda.synchronize()
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record()
+        g.replay()
+        g.replay()
+        s1.record()
+        torch.cuda.synchronize()
+        us = s0.elapsed_time(s1) * 1e3 / (6 * copies)
+        out[name] = {"rows": rows, "k": k, "us": round(us, 2), "gb_s": round(rows * k * 2 / us / 1e3, 1)}
+        del mats
+        torch.cuda.empty_cache()
+    return out
+
+
+def decode_timeline(model, cfg, batch):
+    """One decode step replayed from its CUDA graph under the kineto tracer: for every kernel its
+    start, its duration and the time to the next kernel's start.  Under programmatic dependent
+    launch kernels overlap (a kernel starts while its predecessor drains and waits inside), so
+    the start-to-start column, not the durations, adds up to the step."""
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+    from simple_inference_b200.engine import StepEntry
+    cache, runner = build_runner(model, batch)
+    fill_context(cache, runner, batch, cfg.vocab_size, seed=batch)
+
+    def one(i):
+        runner.step([StepEntry(b, [(i * 7 + b) % 1000], [0]) for b in range(batch)])
+    for i in range(5):
+        one(i)
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for i in range(3):
+            one(10 + i)
+        torch.cuda.synchronize()
+    ev = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA
+          and "memcpy" not in e.name.lower() and "memset" not in e.name.lower()]
+    ev.sort(key=lambda e: e.time_range.start)
+    ev = ev[-(len(ev) // 3):]   # the last of the three steps
+    t0, total = ev[0].time_range.start, ev[-1].time_range.end - ev[0].time_range.start
+    rows = [(e.name.split("(")[0].replace("void ", "").replace("si::", "")[:48],
+             e.time_range.start - t0, e.time_range.end - e.time_range.start) for e in ev]
+    lines = [f"decode step, batch {batch}, context {DECODE_CONTEXT}, {cfg.num_hidden_layers} layers: "
+             f"{len(rows)} kernels, {total:.1f} us from the first kernel's start to the last one's end",
+             "by kernel: share of the step (start to next start), launches, mean duration, mean start-to-start"]
+    agg = {}
+    for i, (name, start, dur) in enumerate(rows):
+        nxt = rows[i + 1][1] if i + 1 < len(rows) else total
+        a = agg.setdefault(name, [0, 0.0, 0.0])
+        a[0] += 1; a[1] += dur; a[2] += nxt - start
+    for name, (n, dur, wall) in sorted(agg.items(), key=lambda kv: -kv[1][2]):
+        lines.append(f"  {100 * wall / total:5.1f} %  n={n:3d}  dur {dur / n:7.2f} us  start-to-start {wall / n:7.2f} us  {name}")
+    k = len(rows) // 2
+    while k < len(rows) - 10 and "rmsnorm" not in rows[k][0]:
+        k += 1
+    lines.append("one layer from the middle of the step: start (us), duration (us), kernel")
+    for name, start, dur in rows[k:k + 9]:
+        lines.append(f"  {start:9.2f}  {dur:7.2f}  {name}")
+    del runner, cache
+    torch.cuda.empty_cache()
+    return "\n".join(lines)
+
+
 def check_against_eager(runner, cache, batch, tokens):
     """Outside the timed region: one more step replayed from the graph, then the same tokens at
     the same positions run eagerly (their keys and values land in the same slots again), and the
@@ -399,9 +501,12 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--no-workloads", action="store_true",
                     help="skip the 1B continuous-batching and 8B long-context workloads")
-    ap.add_argument("--only", choices=["decode", "prefill"],
+    ap.add_argument("--only", choices=["decode", "prefill", "products"],
                     help="run one part and print a short record (for profiling; not the contract line)")
     ap.add_argument("--eager", action="store_true", help="no CUDA graphs (for kernel-level profiles)")
+    ap.add_argument("--timeline", action="store_true",
+                    help="with --only decode: the kernels of one replayed step with their real start "
+                         "times (kineto), as text")
     ap.add_argument("--context", type=int, default=None,
                     help="with --only decode: tokens each request holds (default 2048)")
     ap.add_argument("--prefill-tokens", type=int, default=None,
@@ -435,10 +540,18 @@ def main() -> int:
     full_layers = config["num_hidden_layers"]
     if args.layers:
         config["num_hidden_layers"] = args.layers
+    if args.only == "products":
+        from simple_inference_b200.config.registry import architecture_of
+        cfg = architecture_of(config).config_class.from_dict(config)
+        print(json.dumps(time_products(cfg, args.batch)))
+        return 0
     cfg, model = random_model(config, seed=0, dtype="bfloat16", device="cuda:0")
     layer_params, head_params = matmul_params(cfg)
     weight_bytes = 2 * (layer_params + head_params)
 
+    if args.only == "decode" and args.timeline:
+        print(decode_timeline(model, cfg, args.batch))
+        return 0
     if args.only == "decode":
         ms, launches, _, _, _ = time_decode(model, cfg, args.batch, args.steps, args.warmup)
         print(json.dumps({"only": "decode", "batch": args.batch, "context": DECODE_CONTEXT,
