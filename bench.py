@@ -177,9 +177,14 @@ def time_products(cfg, batch):
         x = torch.randn(batch, k, device=dev).bfloat16()
         y = torch.empty(batch, n, device=dev, dtype=torch.float32 if kind == "logits" else torch.bfloat16)
 
+        y2 = torch.empty(batch, rows, device=dev, dtype=torch.bfloat16) if kind == "swiglu" else None
+
         def run(w):
             if kind == "swiglu" and ops.can_fuse_swiglu(x, w):
                 ops.linear_swiglu(x, w, y)
+            elif kind == "swiglu":   # between the two fused kernels: the product, then the activation
+                ops.linear(x, w, y2)
+                ops.swiglu(y2, y)
             elif kind == "residual":
                 ops.linear_for_residual(x, w, ws, "bench", True)
             else:
