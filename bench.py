@@ -512,6 +512,8 @@ def main() -> int:
     ap.add_argument("--timeline", action="store_true",
                     help="with --only decode: the kernels of one replayed step with their real start "
                          "times (kineto), as text")
+    ap.add_argument("--shape", choices=["3b", "1b", "8b"], default="3b",
+                    help="with --only: the layer sizes (Llama 3.2 3B, 3.2 1B or 3.1 8B)")
     ap.add_argument("--context", type=int, default=None,
                     help="with --only decode: tokens each request holds (default 2048)")
     ap.add_argument("--prefill-tokens", type=int, default=None,
@@ -542,6 +544,8 @@ def main() -> int:
         return 1
     pk, pk_src = peaks()
     config = dict(LLAMA_3_2_3B)
+    if args.only and args.shape != "3b":
+        config = dict(LLAMA_3_2_1B if args.shape == "1b" else LLAMA_3_1_8B)
     full_layers = config["num_hidden_layers"]
     if args.layers:
         config["num_hidden_layers"] = args.layers
