@@ -44,7 +44,8 @@ constexpr uint32_t T2_STAGE_BYTES = T2_SUB * T2_SUB_BYTES;
 constexpr uint32_t T2_TMEM_COLS = 512;
 constexpr uint32_t T2_SMEM_BYTES = T2_STAGES * T2_STAGE_BYTES + 1024 + 256;
 
-enum { T2_EPI_BF16 = 0, T2_EPI_SWIGLU = 2 };
+enum { T2_EPI_BF16 = 0, T2_EPI_SWIGLU = 2, T2_EPI_PARTIAL = 4 };
+constexpr int T2_MAX_SPLITS = 8;
 enum { T2_TIMEOUT_PRODUCER = 1, T2_TIMEOUT_MMA = 2, T2_TIMEOUT_EPILOGUE = 3 };
 
 __device__ __forceinline__ bool t2_wait(uint32_t bar, uint32_t parity, int* status, int code) {
@@ -98,8 +99,9 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
 template <int EPI, int BN>
 __global__ void __launch_bounds__(T2_THREADS, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-                bf16* __restrict__ out, int ldo, int M, int n_out, int K, int up_row0,
+                void* __restrict__ out_any, int ldo, int M, int n_out, int K, int up_row0, int splits,
                 int* __restrict__ status) {
+  bf16* const out = reinterpret_cast<bf16*>(out_any);
   constexpr int TILE_N_OUT = (EPI == T2_EPI_SWIGLU) ? BN / 2 : BN;
   constexpr uint32_t STAGE_TX_BYTES = 2 * (T2_A_BYTES + (BN / 2) * T2_BK * 2);  // both blocks' loads
   extern __shared__ uint8_t smem_raw[];
@@ -120,6 +122,16 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
   const int n_tiles = tiles_m * tiles_n;
   const int k_boxes = (K + T2_BK - 1) / T2_BK;
   const int k_blocks = (k_boxes + T2_SUB - 1) / T2_SUB;  // stages per tile
+  // A unit is (tile, k-range): unit u works on tile u % n_tiles over stages [kb0, kb1) of part
+  // u / n_tiles.  One part (splits == 1) unless the epilogue writes partial sums.
+  const int n_units = n_tiles * splits;
+  auto part_of = [&](int u, int& tile, int& kb0, int& kb1) {
+    tile = u % n_tiles;
+    const int part = u / n_tiles;
+    kb0 = (int)((long long)part * k_blocks / splits);
+    kb1 = (int)((long long)(part + 1) * k_blocks / splits);
+    return part;
+  };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < T2_STAGES; ++s) {
@@ -153,12 +165,14 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
       const uint32_t full_first = map_to_rank(full0, 0);  // the first block counts the bytes
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = pair; ok && tile < n_tiles; tile += n_pairs) {
+      for (int u = pair; ok && u < n_units; u += n_pairs) {
+        int tile, kb0, kb1;
+        part_of(u, tile, kb0, kb1);
         const int m0 = (tile % tiles_m) * 2 * T2_BM + rank * T2_BM;  // m fastest: neighbours share W
         const int n0 = (tile / tiles_m) * TILE_N_OUT;
         const int w_row = (EPI == T2_EPI_SWIGLU) ? (rank == 0 ? n0 : up_row0 + n0)
                                                  : n0 + (int)rank * (BN / 2);
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const uint32_t s = it % T2_STAGES, ph = (it / T2_STAGES) & 1u;
           if (!t2_wait(empty0 + 8 * s, ph ^ 1u, status, T2_TIMEOUT_PRODUCER)) { ok = false; break; }
           const int nsub = k_boxes - kb * T2_SUB < T2_SUB ? k_boxes - kb * T2_SUB : T2_SUB;
@@ -176,12 +190,14 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
       constexpr uint32_t idesc = umma_idesc(2 * T2_BM, BN);
       uint32_t it = 0, acc_it = 0;
       bool ok = true;
-      for (int tile = pair; ok && tile < n_tiles; tile += n_pairs, ++acc_it) {
+      for (int u = pair; ok && u < n_units; u += n_pairs, ++acc_it) {
+        int tile, kb0, kb1;
+        part_of(u, tile, kb0, kb1);
         const uint32_t buf = acc_it & 1u, aph = (acc_it >> 1) & 1u;
         if (!t2_wait(acc_empty0 + 8 * buf, aph ^ 1u, status, T2_TIMEOUT_MMA)) break;
         tmem_fence_after();
         const uint32_t d_tmem = tmem_base + buf * 256;
-        for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const uint32_t s = it % T2_STAGES, ph = (it / T2_STAGES) & 1u;
           if (!t2_wait(full0 + 8 * s, ph, status, T2_TIMEOUT_MMA)) { ok = false; break; }
           tmem_fence_after();
@@ -191,7 +207,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
             const uint64_t da = umma_desc(a_src), db = umma_desc(a_src + T2_A_BYTES);
 #pragma unroll
             for (int k = 0; k < T2_BK / 16; ++k)
-              umma_bf16_pair(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb | j | k) != 0 ? 1u : 0u);
+              umma_bf16_pair(d_tmem, da + 2 * k, db + 2 * k, idesc, (kb != kb0 || (j | k) != 0) ? 1u : 0u);
           }
           umma_commit_pair(empty0 + 8 * s);
         }
@@ -203,7 +219,9 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
     const int quarter = warp & 3;
     const uint32_t acc_empty_first = map_to_rank(acc_empty0, 0);
     uint32_t acc_it = 0;
-    for (int tile = pair; tile < n_tiles; tile += n_pairs, ++acc_it) {
+    for (int u = pair; u < n_units; u += n_pairs, ++acc_it) {
+      int tile, kb0, kb1;
+      const int part = part_of(u, tile, kb0, kb1);
       const uint32_t buf = acc_it & 1u, aph = (acc_it >> 1) & 1u;
       if (!t2_wait(acc_full0 + 8 * buf, aph, status, T2_TIMEOUT_EPILOGUE)) break;
       tmem_fence_after();
@@ -234,6 +252,25 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant
                 for (int i = 0; i < 8; ++i) w8[i] = v[j * 8 + i];
                 store8<bf16>(orow + c * 32 + j * 8, w8);
               }
+            }
+          }
+        }
+      } else if (EPI == T2_EPI_PARTIAL) {
+        // float32 partial sums of this k-range into slice `part` of out[splits][M][ldo]
+        float* prow = reinterpret_cast<float*>(out_any) + ((size_t)part * M + row) * ldo + n0;
+#pragma unroll 1
+        for (int c = 0; c < TILE_N_OUT / 16; ++c) {
+          uint32_t a[16];
+          tmem_ld16(taddr + c * 16, a);
+          tmem_ld_wait();
+          if (row < M) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const int col = n0 + c * 16 + j * 4;
+              if (col < n_out)   // n_out is a multiple of 8
+                *reinterpret_cast<float4*>(prow + c * 16 + j * 4) =
+                    make_float4(__uint_as_float(a[j * 4]), __uint_as_float(a[j * 4 + 1]),
+                                __uint_as_float(a[j * 4 + 2]), __uint_as_float(a[j * 4 + 3]));
             }
           }
         }
@@ -319,13 +356,15 @@ static int choose_bn2(int M, int N, int n_pairs) {
 }
 
 template <int EPI, int BN>
-static int launch_tc2(const CUtensorMap& map_x, const CUtensorMap& map_w, bf16* out, int ldo, int M,
-                      int N, int K, int up_row0, int* status, int n_sms, cudaStream_t stream) {
+static int launch_tc2(const CUtensorMap& map_x, const CUtensorMap& map_w, void* out, int ldo, int M,
+                      int N, int K, int up_row0, int splits, int* status, int n_sms,
+                      cudaStream_t stream) {
   SI_ALLOW_DYNAMIC_SMEM((gemm_tc2_kernel<EPI, BN>), T2_SMEM_BYTES);
   constexpr int tile_n = EPI == T2_EPI_SWIGLU ? BN / 2 : BN;
-  const int n_tiles = ((M + 2 * T2_BM - 1) / (2 * T2_BM)) * ((N + tile_n - 1) / tile_n);
+  const long long n_units =
+      (long long)((M + 2 * T2_BM - 1) / (2 * T2_BM)) * ((N + tile_n - 1) / tile_n) * splits;
   int pairs = n_sms / 2;
-  if (pairs > n_tiles) pairs = n_tiles;
+  if (pairs > n_units) pairs = (int)n_units;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(2 * pairs);
   cfg.blockDim = dim3(T2_THREADS);
@@ -341,7 +380,7 @@ static int launch_tc2(const CUtensorMap& map_x, const CUtensorMap& map_w, bf16* 
   cfg.attrs = attr;
   cfg.numAttrs = 2;
   cudaError_t e = cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<EPI, BN>, map_x, map_w, out, ldo, M, N, K,
-                                     up_row0, status);
+                                     up_row0, splits, status);
   return e == cudaSuccess ? SI_OK : (int)e;
 }
 
@@ -369,14 +408,14 @@ SI_API int si_gemm_tc2_bf16(const void* X, int ldx, const void* W, void* out, in
   if (!make_bf16_map(&map_x, X, M, K, ldx, T2_BM)) return SI_ERR_UNSUPPORTED;
   if (epilogue == T2_EPI_SWIGLU) {
     if (!make_bf16_map(&map_w, W, 2 * N, K, K, 128)) return SI_ERR_UNSUPPORTED;
-    return launch_tc2<T2_EPI_SWIGLU, 256>(map_x, map_w, (bf16*)out, ldo, M, N, K, N, status, n_sms,
+    return launch_tc2<T2_EPI_SWIGLU, 256>(map_x, map_w, out, ldo, M, N, K, N, 1, status, n_sms,
                                           stream);
   }
   const int bn = choose_bn2(M, N, n_sms / 2);
   if (!make_bf16_map(&map_w, W, N, K, K, bn / 2)) return SI_ERR_UNSUPPORTED;
 #define SI_T2_CASE(W)                                                                          \
   case W:                                                                                      \
-    return launch_tc2<T2_EPI_BF16, W>(map_x, map_w, (bf16*)out, ldo, M, N, K, 0, status, n_sms, \
+    return launch_tc2<T2_EPI_BF16, W>(map_x, map_w, out, ldo, M, N, K, 0, 1, status, n_sms, \
                                       stream)
   switch (bn) {
     SI_T2_CASE(256);
@@ -388,8 +427,66 @@ SI_API int si_gemm_tc2_bf16(const void* X, int ldx, const void* W, void* out, in
     SI_T2_CASE(160);
     SI_T2_CASE(144);
     default:
-      return launch_tc2<T2_EPI_BF16, 128>(map_x, map_w, (bf16*)out, ldo, M, N, K, 0, status, n_sms,
+      return launch_tc2<T2_EPI_BF16, 128>(map_x, map_w, out, ldo, M, N, K, 0, 1, status, n_sms,
                                           stream);
   }
 #undef SI_T2_CASE
+}
+
+// Into how many k-ranges si_gemm_tc2_partial should cut the product of M rows, N weight rows and
+// K columns, for a consumer that adds float32 slices anyway (the RMSNorm after a projection
+// that feeds the residual stream).  With few rows a product has fewer 256 x 256 tiles than the
+// GPU has pairs of SMs, and one tile's pass over K bounds its time; cutting K fills the pairs.
+// Every further range costs a float32 slice of M x N that is written and read again.  Returns
+// 1 where cutting does not pay: the caller then takes the ordinary product.
+SI_API int si_gemm_tc2_splits(int M, int N, int K) {
+  using namespace si;
+  if (M <= 0 || N <= 0 || K <= 0) return 1;
+  int dev = 0, n_sms = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess ||
+      cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n_sms < 2)
+    return 1;
+  const int pairs = n_sms / 2;
+  const long long tiles = (long long)((M + 2 * T2_BM - 1) / (2 * T2_BM)) * ((N + 255) / 256);
+  const int stages = ((K + T2_BK - 1) / T2_BK + T2_SUB - 1) / T2_SUB;
+  // microseconds: a stage of a 256-wide tile, a unit's fixed cost, and the slices' way through
+  // L2 and the norm (bytes / 2.5 TB/s, once written and once read)
+  const double t_stage = 0.75, t_unit = 2.5;
+  int best = 1;
+  double best_time = 1e30;
+  for (int s = 1; s <= T2_MAX_SPLITS && stages / s >= 2; ++s) {
+    const long long rounds = (tiles * s + pairs - 1) / pairs;
+    double t = (double)rounds * ((double)((stages + s - 1) / s) * t_stage + t_unit);
+    if (s > 1) t += 2.0 * (double)s * M * N * 4.0 / 2.5e6;
+    if (t < best_time - 1e-9) {
+      best_time = t;
+      best = s;
+    }
+  }
+  return best;
+}
+
+// float32 partial sums of X[M, K] W[N, K]^T over `splits` k-ranges: out[splits][M][ldo], slice p
+// holding range p, to be added in order.  Same conditions as si_gemm_tc2_bf16; ldo a multiple of 4.
+SI_API int si_gemm_tc2_partial(const void* X, int ldx, const void* W, void* out, int ldo, int M, int N,
+                               int K, int splits, int* status, cudaStream_t stream) {
+  using namespace si;
+  if (!X || !W || !out || !status || M < 0 || N <= 0 || K <= 0 || ldx < K || ldo < N || splits < 1)
+    return SI_ERR_ARG;
+  if (K % 8 != 0 || N % 8 != 0 || ldx % 8 != 0 || ldo % 4 != 0) return SI_ERR_UNSUPPORTED;
+  if (splits > T2_MAX_SPLITS) return SI_ERR_TOO_LARGE;
+  if (((uintptr_t)X | (uintptr_t)W | (uintptr_t)out) & 15) return SI_ERR_ARG;
+  if (M == 0) return SI_OK;
+  int dev = 0, n_sms = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e == cudaSuccess) e = cudaDeviceGetAttribute(&n_sms, cudaDevAttrMultiProcessorCount, dev);
+  if (e != cudaSuccess) return (int)e;
+  if (n_sms < 2) return SI_ERR_UNSUPPORTED;
+  const int stages = ((K + T2_BK - 1) / T2_BK + T2_SUB - 1) / T2_SUB;
+  if (splits > stages) return SI_ERR_ARG;   // every slice must get at least one stage
+  CUtensorMap map_x, map_w;
+  if (!make_bf16_map(&map_x, X, M, K, ldx, T2_BM)) return SI_ERR_UNSUPPORTED;
+  if (!make_bf16_map(&map_w, W, N, K, K, 128)) return SI_ERR_UNSUPPORTED;
+  return launch_tc2<T2_EPI_PARTIAL, 256>(map_x, map_w, out, ldo, M, N, K, 0, splits, status, n_sms,
+                                         stream);
 }

@@ -110,7 +110,16 @@ def _p(t: torch.Tensor | None) -> ctypes.c_void_p:
     return _c_void_p(0 if t is None else t.data_ptr())
 
 
+# The current stream's handle, asked for once per kernel launch: torch's own binding for it costs
+# a fraction of a microsecond, torch.cuda.current_stream() (device look-ups, an object per call)
+# some ten times that, which showed as a third of the host time of a step of 250 launches.
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_raw_device = getattr(torch._C, "_cuda_getDevice", None)
+
+
 def _stream() -> ctypes.c_void_p:
+    if _raw_stream is not None and _raw_device is not None:
+        return _c_void_p(_raw_stream(_raw_device()))
     return _c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
@@ -296,7 +305,8 @@ def linear_for_residual(x: torch.Tensor, weight: torch.Tensor, ws, tag: str,
 
     With few rows and a consumer that takes them (``partial_ok``), the weight-streaming kernel
     cuts the k-range across blocks so that a narrow matrix still keeps every SM fetching, and
-    returns ``PartialSums``; otherwise an ordinary tensor in ``x``'s dtype.  ``ws`` is the
+    returns ``PartialSums``; so does the tcgen05 kernel on pairs of SMs where a product of a few
+    hundred rows has too few tiles for the pairs; otherwise an ordinary tensor in ``x``'s dtype.  ``ws`` is the
     step's workspace, ``tag`` names the buffers.
     """
     m, k = x.shape
@@ -313,10 +323,24 @@ def linear_for_residual(x: torch.Tensor, weight: torch.Tensor, ws, tag: str,
             _check(core().si_gemm_skinny_bf16(_p(x), x.stride(0), _p(weight), _p(slices), n,
                                               m, n, k, 4, _stream()), "gemm_skinny_partial")
             return PartialSums(slices, x.dtype)
+    if partial_ok and _tc_ok(x, weight, n):   # from 96 rows on
+        # few 256-row tiles for the pairs of SMs: cut K across them where that pays
+        splits = min(core().si_gemm_tc2_splits(m, n, k), max(WIDE_PART_ROWS // m, 1))
+        if splits > 1:
+            _dev(x, weight)
+            if weight.shape[1] != k or x.dtype != weight.dtype:
+                raise KernelError("linear_for_residual: shapes or dtypes do not fit")
+            slices = ws.get(tag + ".wide_parts", (splits * m, n), torch.float32,
+                            row_cap=WIDE_PART_ROWS).view(splits, m, n)
+            _check(core().si_gemm_tc2_partial(_p(x), x.stride(0), _p(weight), _p(slices), n, m, n, k,
+                                              splits, _p(status_tensor(x.device)), _stream()),
+                   "gemm_tc2_partial")
+            return PartialSums(slices, x.dtype)
     out = ws.get(tag, (m, n), x.dtype)
     return linear(x, weight, out)
 
 
+WIDE_PART_ROWS = 4096   # rows of float32 slices kept for a tcgen05 product cut along k (all slices together)
 SKINNY_MAX_SPLITS = 8   # most k-ranges the weight-streaming product cuts a matrix into
 
 

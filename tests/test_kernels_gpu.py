@@ -529,6 +529,54 @@ def test_tensor_memory_product_on_sm_pairs(ops, m, n, k):
     assert (fused.float() - want).abs().max() < 8e-3 * max(1.0, float(want.abs().max()))
 
 
+@pytest.mark.parametrize("m,n,k,splits", [(256, 512, 512, 2), (300, 264, 1000, 3), (512, 3072, 3072, 3),
+                                          (700, 2048, 8192, 8), (257, 40, 2048, 5)])
+def test_tensor_memory_product_cut_along_k(ops, m, n, k, splits):
+    """The product on pairs of SMs with its k-range cut into float32 slices (for the few-hundred-row
+    portions whose tiles do not fill the pairs): the slices add up to the product, and the norm
+    given the slices does what it does given their rounded sum."""
+    g = gen(12)
+    x = (torch.randn(m, k, device=dev(), generator=g) * 0.5).bfloat16()
+    w = (torch.randn(n, k, device=dev(), generator=g) * 0.1).bfloat16()
+    ref = x.float() @ w.float().T
+    slices = torch.full((splits, m, n), float("nan"), device=dev())
+    code = ops.core().si_gemm_tc2_partial(
+        ops._p(x), x.stride(0), ops._p(w), ops._p(slices), n, m, n, k, splits,
+        ops._p(ops.status_tensor(dev())), ops._stream())
+    assert code == 0
+    ops.check_status()
+    assert torch.isfinite(slices).all(), "every element of every slice is written"
+    assert (slices.sum(0) - ref).abs().max() < 1e-4 * max(1.0, float(ref.abs().max()))
+    parts = ops.PartialSums(slices, torch.bfloat16)
+    whole = parts.tensor()
+    gain = 1 + 0.1 * torch.randn(n, device=dev(), generator=g)
+    res = torch.randn(m, n, device=dev(), generator=g)
+    r1, r2 = res.clone(), res.clone()
+    o1 = torch.empty(m, n, device=dev(), dtype=torch.bfloat16)
+    o2 = torch.empty_like(o1)
+    ops.rmsnorm(r1, gain, 1e-5, o1, delta=parts)
+    ops.rmsnorm(r2, gain, 1e-5, o2, delta=whole)
+    assert torch.equal(r1, r2) and torch.equal(o1, o2)
+
+
+def test_residual_product_of_a_few_hundred_rows_is_cut_where_it_pays(ops):
+    from simple_inference_b200.engine.batch import Workspace
+    g = gen(13)
+    m, n, k = 512, 3072, 8192
+    x = (torch.randn(m, k, device=dev(), generator=g) * 0.5).bfloat16()
+    w = (torch.randn(n, k, device=dev(), generator=g) * 0.1).bfloat16()
+    ws = Workspace(dev(), 2048)
+    got = ops.linear_for_residual(x, w, ws, "t", True)
+    ops.check_status()
+    splits = ops.core().si_gemm_tc2_splits(m, n, k)
+    assert 1 < splits <= 8, "24 tiles for 74 pairs of SMs and 64 stages each: cutting pays"
+    assert isinstance(got, ops.PartialSums) and got.slices.shape == (splits, m, n)
+    plain = ops.linear_for_residual(x, w, ws, "u", False)
+    assert (got.tensor().float() - plain.float()).abs().max() <= 2 ** -6 * float(plain.float().abs().max())
+    # a product with tiles enough for every pair is left whole
+    assert ops.core().si_gemm_tc2_splits(2048, 16384, 3072) == 1
+
+
 @pytest.mark.parametrize("m,n,k", [(128, 256, 64), (130, 264, 72), (96, 40, 8), (300, 5120, 3072),
                                    (2048, 3072, 8192), (1000, 331 * 8, 120)])
 def test_tensor_memory_product_for_many_rows(ops, m, n, k):
