@@ -102,7 +102,32 @@ sample_kernel(const float* __restrict__ logits, int vocab, int ld,
 
   if (!(temp > 0.0f)) {  // greedy
     ArgBest b{-INFINITY, 0x7fffffff};
-    for (int v = tid; v < vocab; v += SAMPLE_THREADS) b = better(b, ArgBest{row[v], v});
+    int done = 0;
+    if ((reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+      // four 16-byte loads in flight per thread: a row of 128k logits is 31 such loads a thread,
+      // and one after the other they took 19 us
+      const float4* row4 = reinterpret_cast<const float4*>(row);
+      const int n4 = vocab >> 2;
+      for (int i = tid; i < n4; i += 4 * SAMPLE_THREADS) {
+        float4 q[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int j = i + u * SAMPLE_THREADS;
+          q[u] = j < n4 ? row4[j] : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (i + u * SAMPLE_THREADS >= n4) break;   // never let a filler's index in
+          const int v = (i + u * SAMPLE_THREADS) * 4;
+          b = better(b, ArgBest{q[u].x, v});
+          b = better(b, ArgBest{q[u].y, v + 1});
+          b = better(b, ArgBest{q[u].z, v + 2});
+          b = better(b, ArgBest{q[u].w, v + 3});
+        }
+      }
+      done = n4 << 2;
+    }
+    for (int v = done + tid; v < vocab; v += SAMPLE_THREADS) b = better(b, ArgBest{row[v], v});
     b = block_argbest(b, sv, sidx);
     if (tid == 0) out[r] = (b.i == 0x7fffffff) ? -1 : b.i;  // -1: no comparable logit (NaN row)
     return;

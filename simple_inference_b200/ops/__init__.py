@@ -575,8 +575,11 @@ def attention_prefill_wide(q: torch.Tensor, pool: torch.Tensor, ctx, plan, group
 def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
            top_p: torch.Tensor, seed: torch.Tensor, stream_id: torch.Tensor,
            counter: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-    """One token per row of float32 logits; per-row parameters (see sampling.cu)."""
-    _dev(logits, temperature, top_k, top_p, seed, stream_id, counter, out)
+    """One token per row of float32 logits; per-row parameters (see sampling.cu).  The rows of
+    ``logits`` may be further apart than the vocabulary is wide."""
+    _dev(temperature, top_k, top_p, seed, stream_id, counter, out)
+    if not logits.is_cuda or logits.dim() != 2 or logits.stride(1) != 1 or logits.device != out.device:
+        raise KernelError("sample: logits must be a matrix on the GPU of its parameters, rows contiguous")
     n, vocab = logits.shape
     if logits.dtype != torch.float32 or temperature.dtype != torch.float32 or \
             top_p.dtype != torch.float32:

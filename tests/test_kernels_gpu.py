@@ -418,6 +418,21 @@ def test_sampling_kernel_against_plain_sampler(ops):
     assert int(got[0]) == int(big[0].argmax())
     kept = torch.isfinite(plain_llama.filter_logits(big[1].cpu(), 0.7, 40, 0.95))
     assert bool(kept[int(got[1])])
+    # greedy rows read 16 bytes at a time where they can: ties go to the lowest index, a row of
+    # NaN gives -1, rows that start off a 16-byte boundary and widths that are no multiple of 4
+    for vocab, ld in ((128256, 128256), (5003, 5003), (5003, 5004), (7, 7), (4099, 4100)):
+        rows = torch.randn(5, ld, device=dev(), generator=gen(vocab))
+        rows[1, :vocab] = float("nan")
+        rows[2, :vocab] = 0.25                      # all equal: index 0
+        rows[3, vocab - 1] = 50.0                   # the last one, in the scalar tail
+        rows[4, [3, vocab // 2, vocab - 2]] = 60.0  # a tie: the first of them
+        if ld > vocab:
+            rows[:, vocab:] = 1000.0                # beyond the vocabulary: never read
+        zero = torch.zeros(5, device=dev())
+        zi = torch.zeros(5, device=dev(), dtype=torch.int32)
+        got = torch.empty(5, device=dev(), dtype=torch.int32)
+        ops.sample(rows[:, :vocab], zero, zi, torch.ones(5, device=dev()), zi, zi, zi, got)
+        assert got.tolist() == [int(rows[0, :vocab].argmax()), -1, 0, vocab - 1, 3], (vocab, ld)
 
 
 def test_kernels_refuse_what_they_cannot_take(ops):
