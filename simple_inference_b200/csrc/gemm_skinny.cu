@@ -18,15 +18,16 @@
 //   * The ring is filled BEFORE the wait on the preceding kernel (weights are never
 //     written), so under programmatic dependent launch the weights of this product
 //     stream in while the kernel before it (a norm, attention's join) still runs.
-//   * A product runs as at most two blocks an SM, all resident from the start, each
-//     working through its share of the row tiles with its rings running on from tile
-//     to tile.  That leaves half of every SM to the blocks of the NEXT product, which
-//     are let in at once (the trigger is the kernel's first instruction) and fill
-//     their rings while this one still streams: the weight stream does not stop at a
-//     kernel boundary.
+//   * A product runs as at most four blocks an SM (48 KB of rings each), all resident from
+//     the start, each working through its share of the row tiles with its rings running on
+//     from tile to tile.  The trigger for the NEXT kernel is the block's first instruction:
+//     as this product's blocks leave, the next product's blocks settle in their place and
+//     fill their own rings while this one still streams, so the weight stream does not stop
+//     at a kernel boundary.  (Two blocks an SM, leaving half of each SM to the successor from
+//     the start, was slower: a product needs the depth more than the overlap.)
 //   * The k-range of the products that feed the residual stream (which the next
 //     RMSNorm adds up anyway) is cut across blocks, so that a matrix of 3072 rows
-//     still gives every SM its two blocks.  Partial sums go out as float32 slices
+//     still fills the SMs.  Partial sums go out as float32 slices
 //     [splits, M, N] that the consumer adds in a fixed order.
 //
 // The weights are the 16-row operand of mma.sync m16n8k16 and the tokens the 8-wide
@@ -181,9 +182,9 @@ skinny_gemm_kernel(const bf16* __restrict__ X, int ldx, const bf16* __restrict__
     cp_async_commit_group();   // an empty group keeps the count of groups uniform
   };
 
-  // All blocks of this product are resident from the start (the grid is no larger than two
-  // blocks an SM), so the kernel after it may be scheduled at once: its blocks settle in the
-  // other half of each SM and fill their own rings while this product still runs.
+  // All blocks of this product are resident from the start (the grid is no larger than four
+  // blocks an SM), so the kernel after it may be scheduled at once: its blocks settle where
+  // this product's blocks leave and fill their own rings while the rest still run.
   if (SK_EARLY_TRIGGER) pdl_trigger();
 #pragma unroll
   for (int i = 0; i < SK_STAGES; ++i) fetch();   // weights are never written: ask before waiting
@@ -383,7 +384,7 @@ static int launch_skinny(const void* X, int ldx, const void* W, void* out, int l
 }  // namespace si
 
 // How many slices of partial sums si_gemm_skinny_bf16 writes for epilogue 4 at these sizes:
-// as many k-ranges as still let every block of the product be resident at once (two blocks
+// as many k-ranges as still let every block of the product be resident at once (four blocks
 // an SM), each range no shorter than one round of the four warps.
 SI_API int si_gemm_skinny_splits(int N, int K) {
   using namespace si;
