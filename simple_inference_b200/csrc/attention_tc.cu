@@ -1,4 +1,4 @@
-// Prefill attention on the fifth-generation tensor cores (head size 128, pages of 8 to 64
+// Prefill attention on the fifth-generation tensor cores (head sizes 128 and 64, pages of 8 to 64
 // tokens): the flash-attention forward of the reference (kernels/attention_kernel.py:108-251)
 // over the paged cache, with both matrix products as tcgen05.mma and their results in tensor
 // memory.
@@ -40,18 +40,21 @@
 #error "compile with -DSI_HEAD_DIM=<head size>"
 #endif
 
-#if SI_HEAD_DIM == 128
+#if SI_HEAD_DIM == 128 || SI_HEAD_DIM == 64
 
 namespace si {
 
 typedef __nv_bfloat16 bf16;
-constexpr int TQ = 128, TK = 128, HD = 128;
+constexpr int TQ = 128, TK = 128, HD = SI_HEAD_DIM;
+constexpr int HALVES_TC = HD / 64;                   // 64-column halves of a row: 128 bytes each
 constexpr uint32_t HALF_BYTES_TC = 128 * 128;        // 128 rows x 64 bf16
-constexpr uint32_t TILE_BYTES = 2 * HALF_BYTES_TC;   // 128 x 128 bf16 = 32 KiB
+constexpr uint32_t TILE_BYTES = HALVES_TC * HALF_BYTES_TC;   // 128 x HD bf16: 32 KiB (heads of 128), 16 KiB (64)
+constexpr uint32_t ROW_BYTES_TC = HD * 2;            // a row of a key or value tile
+constexpr uint32_t GROUP_BYTES_TC = 8 * ROW_BYTES_TC;  // eight rows: their halves side by side
 constexpr int ATC_THREADS = 384;  // key producer, S issuer, eight softmax warps, P V issuer, value producer
 constexpr int PV_WARP = 2, V_WARP = 3, SOFTMAX_WARP0 = 4;  // warps 0..3: the light roles, one warpgroup
 constexpr int LIGHT_REGS = 56, SOFTMAX_REGS = 224;     // 128 x 56 + 256 x 224 registers = 63 K of the SM's 64 K
-constexpr int RING = 5;           // K and V tiles share one ring of 32 KiB slots
+constexpr int RING = HD == 128 ? 5 : 8;   // K and V tiles share one ring of slots of a tile each
 constexpr uint32_t ATC_SMEM = 1024 + (1 + RING) * TILE_BYTES + 256;  // Q, the ring, barriers
 
 // Tiles enter the ring in the order the tensor core needs them: K0, K1, V0, K2, V1, ...,
@@ -177,8 +180,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
     int (*tile_pages)[32] = tile_pages_of[my_kind_is_v ? 1 : 0];
     if (warp == 0 && lane == 0) {
       mbar_expect_tx(q_full, TILE_BYTES);
-      tma_load_2d(sQ, &q_map, q_full, h * HD, tok0);
-      tma_load_2d(sQ + HALF_BYTES_TC, &q_map, q_full, h * HD + 64, tok0);
+#pragma unroll
+      for (int half = 0; half < HALVES_TC; ++half)
+        tma_load_2d(sQ + half * HALF_BYTES_TC, &q_map, q_full, h * HD + 64 * half, tok0);
     }
     const int pages_per_tile = TK / page_size;  // at most 16
     const int n_items = 2 * n_tiles;
@@ -221,12 +225,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
       }
       const int n_pages = __popc(__ballot_sync(0xffffffffu, page >= 0));
       if (lane == 0)
-        mbar_expect_tx(slot_full0 + 8 * slot, (uint32_t)n_pages * page_size * 256u);
+        mbar_expect_tx(slot_full0 + 8 * slot, (uint32_t)n_pages * page_size * ROW_BYTES_TC);
       __syncwarp();
       if (page >= 0) {
         // the page's rows of this kv head, both column halves, in one copy (see make_page_map);
-        // in the slot, page i of the tile is page_size * 256 bytes from page i - 1
-        const uint32_t dst = ring + slot * TILE_BYTES + lane * page_size * 256;
+        // in the slot, page i of the tile is page_size rows from page i - 1
+        const uint32_t dst = ring + slot * TILE_BYTES + lane * page_size * ROW_BYTES_TC;
         const int group0 = ((page * 2) * n_kv_heads + kvh) * (page_size >> 3);
         tma_load_5d(dst, &kv_map, slot_full0 + 8 * slot, 0, 0, 0, group0, is_v ? 1 : 0);
       }
@@ -255,8 +259,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
           // Q: two half tiles of 128 rows; K: the halves of every 8-row group side by side
           const uint32_t q_off = (k >> 2) * HALF_BYTES_TC + (k & 3) * 32;
           const uint32_t k_off = (k >> 2) * 1024 + (k & 3) * 32;
-          umma_bf16(tmem_base + b * 128, umma_desc(sQ + q_off), umma_desc(kbase + k_off, 2048), idesc_s,
-                    k != 0 ? 1u : 0u);
+          umma_bf16(tmem_base + b * 128, umma_desc(sQ + q_off), umma_desc(kbase + k_off, GROUP_BYTES_TC),
+                    idesc_s, k != 0 ? 1u : 0u);
         }
         umma_commit(s_full0 + 8 * b);
         umma_commit(slot_empty0 + 8 * slot);
@@ -279,9 +283,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
 #pragma unroll
         for (int k = 0; k < TK / 16; ++k) {  // 16 keys per step: 8 columns of packed P, two 8-row groups of V
           // the set's output adds up over its tiles (tiles b, b + 2, ...): only its first starts anew
-          // V: 16 keys are two 8-row groups 2048 bytes apart; the second column half 1024 bytes on
+          // V: 16 keys are two 8-row groups, a group's second column half 1024 bytes after its first
           umma_bf16_ts(tmem_base + 256 + b * 128, tmem_base + b * 128 + k * 8,
-                       umma_desc_mn(vbase + k * 4096, 1024, 2048), idesc_o, (t >= 2 || k != 0) ? 1u : 0u);
+                       umma_desc_mn(vbase + k * 2 * GROUP_BYTES_TC, 1024, GROUP_BYTES_TC), idesc_o,
+                       (t >= 2 || k != 0) ? 1u : 0u);
         }
         umma_commit(o_full0 + 8 * b);
         umma_commit(slot_empty0 + 8 * slot);
@@ -397,7 +402,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
       l_run += acc.x + acc.y;
     }
 
-    // ---- join the two sets: thread (set, row) writes output columns [64 set, 64 set + 64)
+    // ---- join the two sets: thread (set, row) writes output columns [HD/2 set, HD/2 set + HD/2)
     xmax[0][set][row] = m_run;
     xsum[set][row] = l_run;
     const int n_mine[2] = {(n_tiles + 1) / 2, n_tiles / 2};
@@ -416,12 +421,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map,
       const float w1 = (!two || m1 == -INFINITY) ? 0.0f : ex2_approx(m1 - mm);
       float inv = 1.0f / (xsum[0][row] * w0 + xsum[1][row] * w1);
       if (!ok || *reinterpret_cast<volatile int*>(&failed)) inv = __int_as_float(0x7fc00000);  // make it visible
-      bf16* dst = out + (long long)(tok0 + row) * out_stride + (long long)h * HD + set * 64;
+      bf16* dst = out + (long long)(tok0 + row) * out_stride + (long long)h * HD + set * (HD / 2);
 #pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
+      for (int c = 0; c < HD / 64; ++c) {
         uint32_t r0[32], r1[32];
-        tmem_ld32(tmem_base + 256 + lane_off + set * 64 + c * 32, r0);
-        if (two) tmem_ld32(tmem_base + 384 + lane_off + set * 64 + c * 32, r1);
+        tmem_ld32(tmem_base + 256 + lane_off + set * (HD / 2) + c * 32, r0);
+        if (two) tmem_ld32(tmem_base + 384 + lane_off + set * (HD / 2) + c * 32, r1);
         tmem_ld_wait();
 #pragma unroll
         for (int q8 = 0; q8 < 4; ++q8) {

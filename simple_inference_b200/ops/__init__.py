@@ -541,8 +541,8 @@ WIDE_MIN_QUERIES = 64  # shorter portions stay on the 64-query mma.sync tiles
 
 def wide_prefill_fits(plan, head_dim: int, page_size: int) -> bool:
     """Whether the tcgen05 prefill kernel takes this step's portions: it is written for heads
-    of 128 and pages of 8, 16, 32 or 64 tokens, and pays off from 64 queries a portion."""
-    return head_dim == 128 and page_size in (8, 16, 32, 64) and \
+    of 128 and 64 and pages of 8, 16, 32 or 64 tokens, and pays off from 64 queries a portion."""
+    return head_dim in (64, 128) and page_size in (8, 16, 32, 64) and \
         plan.n_wide > 0 and plan.max_q_len >= WIDE_MIN_QUERIES
 
 

@@ -56,7 +56,19 @@ TINY_D = {
     "rope_theta": 100000.0, "rope_scaling": None, "rms_norm_eps": 2e-5,
     "tie_word_embeddings": False, "max_position_embeddings": 1024, "torch_dtype": "bfloat16",
 }
-TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D}
+# A fifth with heads of 64 in groups of three: the other head size that the tcgen05 attention
+# and the TMA-fed decode attention take.
+TINY_E = {
+    "architectures": ["LlamaForCausalLM"],
+    "num_hidden_layers": 2, "hidden_size": 192, "num_attention_heads": 6,
+    "num_key_value_heads": 2, "head_dim": 64, "intermediate_size": 320, "vocab_size": 411,
+    "rope_theta": 300000.0,
+    "rope_scaling": {"rope_type": "llama3", "factor": 16.0, "low_freq_factor": 1.0,
+                     "high_freq_factor": 4.0, "original_max_position_embeddings": 128},
+    "rms_norm_eps": 1e-5, "tie_word_embeddings": True, "max_position_embeddings": 1024,
+    "torch_dtype": "bfloat16",
+}
+TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": TINY_D, "E": TINY_E}
 
 
 @pytest.fixture(scope="session")

@@ -256,10 +256,10 @@ WIDE_CASES = [
 ]
 
 
+@pytest.mark.parametrize("d", [128, 64])
 @pytest.mark.parametrize("what,lens,starts,ps,hq,hkv,window", WIDE_CASES,
                          ids=[c[0] for c in WIDE_CASES])
-def test_tcgen05_prefill_attention(ops, what, lens, starts, ps, hq, hkv, window):
-    d = 128
+def test_tcgen05_prefill_attention(ops, what, lens, starts, ps, hq, hkv, window, d):
     qkv, pool, ctx, n = paged_case(lens, starts, ps, hq, hkv, d, torch.bfloat16, seed=3)
     assert ops.wide_prefill_fits(ctx.plan, d, ps)
     out = torch.zeros(n, hq * d, device=dev(), dtype=torch.bfloat16)
@@ -272,10 +272,11 @@ def test_tcgen05_prefill_attention(ops, what, lens, starts, ps, hq, hkv, window)
     assert_attention_close(out, ref, what)
 
 
-def test_tcgen05_prefill_finds_one_far_key(ops):
+@pytest.mark.parametrize("d", [128, 64])
+def test_tcgen05_prefill_finds_one_far_key(ops, d):
     """One key per query head, far back and on a page of its own, matches 30 times better
     than the rest: every row's output must be that key's value (7)."""
-    hq, hkv, d, ps = 4, 2, 128, 16
+    hq, hkv, ps = 4, 2, 16
     qkv, pool, ctx, n = paged_case([200, 129], [900, 300], ps, hq, hkv, d, torch.bfloat16, seed=5)
     pool.mul_(0.05)
     table = ctx.block_tables[0]

@@ -57,12 +57,15 @@ def cases(model_folders, tmp_path_factory):
     out = {}
     for name, folder in folders.items():
         cfg, w = plain_llama.read_folder(folder)
-        top = min(cfg["max_position_embeddings"], 420 if name in ("D", "sharpD") else 230)
+        top = min(cfg["max_position_embeddings"], 420 if name in LONG else 230)
         lens = [top, 97, 64, 33, 5, 150][: 6 if top > 128 else 5]
         lens = [min(n, top) for n in lens]
         seqs = [random_ids(n, cfg["vocab_size"], 100 + i) for i, n in enumerate(lens)]
         out[name] = (folder, cfg, w, seqs, [plain_llama.forward(cfg, w, s) for s in seqs])
     return out
+
+
+LONG = ("D", "sharpD", "E")   # head sizes of the Blackwell kernels: prompts long enough to reach them
 
 
 def _tol(table, dtype, what):
@@ -76,10 +79,10 @@ def _check(got, want, dtype, what):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D", "sharp", "sharpD"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "E", "sharp", "sharpD"])
 def test_whole_then_last_32_then_portions(name, dtype, cases, tmp_path):
     folder, cfg, w, seqs, plain = cases[name]
-    with Trace(folder, dtype, tmp_path, max_tokens=512 if "D" in name else 256) as tr:
+    with Trace(folder, dtype, tmp_path, max_tokens=512 if name in LONG else 256) as tr:
         for i, (ids, ref) in enumerate(zip(seqs[:3], plain[:3])):
             n = len(ids)
             # (1) alone and whole, every position wanted
@@ -108,7 +111,7 @@ def test_whole_then_last_32_then_portions(name, dtype, cases, tmp_path):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "sharp", "D", "sharpD"])
+@pytest.mark.parametrize("name", ["A", "B", "sharp", "D", "E", "sharpD"])
 def test_mixed_batches_with_pages_used_again(name, dtype, cases, tmp_path):
     """Up to four live requests, portions of some beside decoded tokens of others, in a pool
     of 320 tokens (20 pages) that the requests need 2.5 times over.  The configurations with
@@ -117,11 +120,11 @@ def test_mixed_batches_with_pages_used_again(name, dtype, cases, tmp_path):
     decoded tokens of other requests while pages change hands."""
     folder, cfg, w, seqs, plain = cases[name]
     lens = [len(s) for s in seqs]
-    pool = 640 if "D" in name else 320
+    pool = 640 if name in LONG else 320
     assert sum((n + 63) // 64 * 64 for n in lens) > pool     # more than the pool: pages come back
     # each request: a prompt part fed in portions, then the rest token by token
     plan = {i: {"prompt": max(2, n - 20 - 3 * i), "fed": 0} for i, n in enumerate(lens)}
-    portion = [9, 2, 200, 5, 128, 2, 64] if "D" in name else [9, 2, 30, 5, 17, 2, 64]
+    portion = [9, 2, 200, 5, 128, 2, 64] if name in LONG else [9, 2, 30, 5, 17, 2, 64]
     waiting = list(range(len(seqs)))
     live: list[int] = []
     got = {i: {} for i in range(len(seqs))}
