@@ -28,6 +28,13 @@ class Sampler:
         self._out = torch.zeros(max_rows, dtype=torch.int32, device=device)
         self._out_host = torch.zeros(max_rows, dtype=torch.int32, pin_memory=pin)
         self._status_host = torch.zeros(1, dtype=torch.int32, pin_memory=pin)
+        self._done = torch.cuda.Event() if pin else None
+        # what the rows held at the last call: while the same requests keep drawing (steady
+        # decoding) only their counters change, and one slice assignment writes those
+        self._last_rows: list[tuple[SamplingParams, int]] | None = None
+        # views of the buffers per number of rows, made once (slicing costs more than sampling's
+        # other host work)
+        self._views: dict[int, tuple] = {}
 
     @property
     def host_bytes(self) -> int:
@@ -47,16 +54,21 @@ class Sampler:
             raise ValueError(f"{n} rows exceed the sampler's capacity {self.max_rows}")
         if n == 0:
             return []
-        f32 = self._np.view(np.float32)
-        u32 = self._np.view(np.uint32)
         m = self.max_rows
-        for i, (p, stream, counter) in enumerate(rows):
-            f32[0 * m + i] = p.temperature
-            self._np[1 * m + i] = p.top_k
-            f32[2 * m + i] = p.top_p
-            u32[3 * m + i] = p.seed & 0xFFFFFFFF
-            u32[4 * m + i] = stream & 0xFFFFFFFF
-            u32[5 * m + i] = counter & 0xFFFFFFFF
+        who = [(p, stream) for p, stream, _ in rows]
+        if who == self._last_rows:
+            self._np.view(np.uint32)[5 * m:5 * m + n] = [c & 0xFFFFFFFF for _, _, c in rows]
+        else:
+            f32 = self._np.view(np.float32)
+            u32 = self._np.view(np.uint32)
+            for i, (p, stream, counter) in enumerate(rows):
+                f32[0 * m + i] = p.temperature
+                self._np[1 * m + i] = p.top_k
+                f32[2 * m + i] = p.top_p
+                u32[3 * m + i] = p.seed & 0xFFFFFFFF
+                u32[4 * m + i] = stream & 0xFFFFFFFF
+                u32[5 * m + i] = counter & 0xFFFFFFFF
+            self._last_rows = who
         self._dev.copy_(self._host, non_blocking=True)
         self.sample_on_device(logits)
         self._out_host[:n].copy_(self._out[:n], non_blocking=True)
@@ -64,7 +76,8 @@ class Sampler:
             # the kernels' status word rides home with the tokens: one synchronisation for both
             status = ops.status_tensor(self.device)
             self._status_host.copy_(status, non_blocking=True)
-            torch.cuda.current_stream().synchronize()
+            self._done.record()
+            self._done.synchronize()
             if int(self._status_host[0]) != 0:
                 ops.check_status(self.device)
         tokens = self._out_host[:n].tolist()
@@ -78,8 +91,11 @@ class Sampler:
         """Draw for the rows of ``logits`` with the options of the last ``sample`` call already
         on the device; the tokens stay on the device (no copy, no synchronisation)."""
         n = logits.shape[0]
-        d = self._dev
-        ops.sample(logits, self._field(d, 0, n).view(torch.float32), self._field(d, 1, n),
-                   self._field(d, 2, n).view(torch.float32), self._field(d, 3, n),
-                   self._field(d, 4, n), self._field(d, 5, n), self._out[:n])
-        return self._out[:n]
+        v = self._views.get(n)
+        if v is None:
+            d = self._dev
+            v = self._views[n] = (self._field(d, 0, n).view(torch.float32), self._field(d, 1, n),
+                                  self._field(d, 2, n).view(torch.float32), self._field(d, 3, n),
+                                  self._field(d, 4, n), self._field(d, 5, n), self._out[:n])
+        ops.sample(logits, *v)
+        return v[6]
