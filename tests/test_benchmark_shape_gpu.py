@@ -7,7 +7,8 @@ all and still print a tokens-per-second figure.
 
 float32 path against the plain model on a short prompt; bfloat16 against the float32 path on
 a 300-token prompt cut three ways; one decode step of 64 sequences at contexts between 1 and
-2,047, replayed from a CUDA graph, against the float32 path.
+2,047 and one of 100 sequences (the rows of the tcgen05 products, cut along k), both replayed
+from CUDA graphs, against the float32 path.
 """
 
 import pytest
@@ -70,7 +71,7 @@ def test_float32_path_equals_the_plain_model_at_these_sizes(folder):
     assert torch.equal(got.argmax(-1), want.argmax(-1))
 
 
-def test_bfloat16_against_the_float32_path_three_cuts_and_64_sequences_decoding(folder):
+def test_bfloat16_against_the_float32_path_three_cuts_and_64_and_100_sequences_decoding(folder):
     from simple_inference_b200.engine import StepEntry
     vocab = SHAPE_3B_TWO_LAYERS["vocab_size"]
     ids = random_ids(300, vocab, 4)
@@ -80,7 +81,7 @@ def test_bfloat16_against_the_float32_path_three_cuts_and_64_sequences_decoding(
 
     def run(dtype, graphs):
         out = {}
-        cache, runner = _runner(folder, dtype, 64, 2048, graphs=graphs)
+        cache, runner = _runner(folder, dtype, 128, 2048, graphs=graphs)
         cache.admit("w", 300)
         out["whole"] = runner.step([StepEntry("w", ids, list(range(300)))]).clone()
         cache.release("w")
@@ -98,7 +99,7 @@ def test_bfloat16_against_the_float32_path_three_cuts_and_64_sequences_decoding(
             cache.release("tail")
         # 64 sequences: all but the last token in steps of at most 2,048 tokens, then ONE decode step
         for i, s in enumerate(seqs):
-            cache.admit(i, len(s))
+            cache.admit(i, len(s) + 1)
         batch, room = [], 2048
         for i, s in enumerate(seqs):
             if len(s) == 1:
@@ -113,6 +114,16 @@ def test_bfloat16_against_the_float32_path_three_cuts_and_64_sequences_decoding(
         out["decode 64"] = runner.step([StepEntry(i, [s[-1]], [0]) for i, s in enumerate(seqs)]).clone()
         if graphs:
             assert 64 in runner._graphs, "the decode step of 64 sequences ran from a captured graph"
+        # 36 more sequences join, then ONE decode step of 100: enough rows for the tcgen05 products,
+        # whose projections into the residual stream are cut along k at these sizes
+        more = [random_ids(2 + (i * 7) % 40, vocab, 900 + i) for i in range(36)]
+        for i, s in enumerate(more):
+            cache.admit(64 + i, len(s) + 1)
+        runner.step([StepEntry(64 + i, s, []) for i, s in enumerate(more)])
+        nxt = random_ids(100, vocab, 77)
+        out["decode 100"] = runner.step([StepEntry(i, [nxt[i]], [0]) for i in range(100)]).clone()
+        if graphs:
+            assert 128 in runner._graphs, "the decode step of 100 sequences ran from a captured graph"
         cache.check()
         return {k: v.float().cpu() for k, v in out.items()}
 
@@ -120,7 +131,8 @@ def test_bfloat16_against_the_float32_path_three_cuts_and_64_sequences_decoding(
     got = run("bfloat16", True)
     spread = _spread(ref["whole"])
     pairs = [("whole", ref["whole"]), ("two portions", ref["whole"]),
-             ("last 16 one by one", ref["whole"][283:]), ("decode 64", ref["decode 64"])]
+             ("last 16 one by one", ref["whole"][283:]), ("decode 64", ref["decode 64"]),
+             ("decode 100", ref["decode 100"])]
     for what, want in pairs:
         diff = float((got[what] - want).abs().max())
         agree = float((got[what].argmax(-1) == want.argmax(-1)).float().mean())

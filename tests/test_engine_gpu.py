@@ -97,6 +97,29 @@ def test_forty_requests_decoding_together(name, model_folders):
     _agree_where_the_plain_model_is_sure(cfg, w, prompts, outs[0], outs[1])
 
 
+@pytest.mark.parametrize("name", ["D", "E"])
+def test_a_hundred_and_ten_requests_decoding_together(name, model_folders):
+    """max_running 128 and 110 short prompts: decoding reaches the graph bucket of 128, whose
+    matrix products have enough rows for the tcgen05 kernels (the projections that feed the
+    residual stream cut along k, their slices added by the norms) inside a captured graph;
+    greedy tokens against the plain model."""
+    cfg, w = plain_llama.read_folder(model_folders[name])
+    prompts = [random_ids(3 + (5 * i) % 40, cfg["vocab_size"], 700 + i) for i in range(110)]
+    outs = []
+    for graphs in (True, False):
+        eng = _engine(model_folders[name], "bfloat16", use_cuda_graphs=graphs, max_running=128,
+                      block_size=16, max_tokens_per_step=512, chunk_size=None, max_seq_len=96)
+        reqs = [eng.add_request(p, 6 + i % 4) for i, p in enumerate(prompts)]
+        live = []
+        while eng.has_work():
+            eng.step()
+            live.append(sum(r.state.value == "decode" for r in eng.scheduler.running))
+        assert max(live) >= 96, "the run must reach the rows of the tcgen05 products"
+        outs.append([r.generated for r in reqs])
+        eng.cache.check()
+    _agree_where_the_plain_model_is_sure(cfg, w, prompts, outs[0], outs[1])
+
+
 def test_temperature_sampling_matches_the_plain_sampler(model_folders):
     """BASELINE's workload for Tiny B: prompts of 1, 9, 40 and 100 ids, portions of 16 mixed
     with decoding, temperature 0.8, seed 0, page size 8."""
