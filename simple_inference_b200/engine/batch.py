@@ -61,6 +61,7 @@ class Workspace:
         self.max_rows = max_rows
         self.max_logit_rows = max_logit_rows if max_logit_rows is not None else max_rows
         self._buffers: dict[tuple[str, torch.dtype], torch.Tensor] = {}
+        self._views: dict[tuple, torch.Tensor] = {}
         self._frozen = False
 
     def freeze(self) -> None:
@@ -68,6 +69,10 @@ class Workspace:
 
     def get(self, tag: str, shape: tuple[int, ...], dtype: torch.dtype,
             row_cap: int | None = None) -> torch.Tensor:
+        vkey = (tag, dtype, shape)
+        view = self._views.get(vkey)
+        if view is not None:   # the same buffer cut the same way as before: no arithmetic, no new view
+            return view
         width = 1
         for s in shape[1:]:
             width *= s
@@ -81,7 +86,12 @@ class Workspace:
             cap = max(shape[0], row_cap if row_cap is not None else self.max_rows)
             buf = torch.empty(max(cap * width, 1), dtype=dtype, device=self.device)
             self._buffers[key] = buf
-        return buf[:numel].view(shape)
+            for k in [k for k in self._views if k[0] == tag and k[1] == dtype]:
+                del self._views[k]   # views of the buffer this one replaces
+        if len(self._views) >= 4096:
+            self._views.clear()
+        view = self._views[vkey] = buf[:numel].view(shape)
+        return view
 
 
 @dataclass
